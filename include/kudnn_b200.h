@@ -1,0 +1,150 @@
+/*
+ * kudnn_b200 — C ABI of the B200 (sm_100a) Linear(+post-op) path.
+ *
+ * This is the boundary the C++ classes KuDNN::Gemm, KuDNN::LinearActivationLayerFWD and
+ * KuDNN::LinearResFWD call into.  Plain pointers, sizes and PODs only; no exceptions cross it.
+ * Every function returns one of the KUDNN_B200_* status codes; the text of the last error of
+ * the calling thread is available from kudnn_b200_last_error().
+ *
+ * One descriptor covers what the three reference classes can express for this path:
+ *     c   = act( alpha * a·b + beta * c + bias )              (rounded to c_dtype as the reference does)
+ *     out = c (+) res                                          (optional second output)
+ * with a [m,k], b [k,n], c / res / out [m,n], bias broadcastable to [m,n], up to three leading
+ * batch dimensions (stride 0 = broadcast), every tensor addressed by element strides.
+ */
+#ifndef KUDNN_B200_H
+#define KUDNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KUDNN_B200_API __attribute__((visibility("default")))
+
+/* Status codes.  0..2 are KuDNN::Status (src/dnn/include/service/kudnn_err_codes.hpp:18-22);
+ * the rest are appended for conditions a CPU library does not have. */
+#define KUDNN_B200_OK 0
+#define KUDNN_B200_UNSUPPORTED 1
+#define KUDNN_B200_BAD_ARGUMENTS 2
+#define KUDNN_B200_ALLOC_FAILED 3
+#define KUDNN_B200_CUDA_ERROR 4
+#define KUDNN_B200_TIMEOUT 5   /* a bounded device-side wait gave up; the context stays usable */
+#define KUDNN_B200_NO_DEVICE 6 /* no sm_100 device, or the CUDA runtime could not be initialised */
+
+/* Element types: the values of KuDNN::Element::TypeT (src/dnn/include/types/kudnn_data_type.hpp:31-39). */
+#define KUDNN_B200_F32 1
+#define KUDNN_B200_F16 2
+#define KUDNN_B200_BF16 3
+
+/* Activations: the values of KuDNN::ActivationFunction (src/dnn/include/operations/kudnn_eltwise.hpp:24-54);
+ * 0 (UNIMPLEMENTED there) means "no activation" here. */
+#define KUDNN_B200_ACT_NONE 0
+#define KUDNN_B200_ACT_RELU 5
+#define KUDNN_B200_ACT_TANH 9
+#define KUDNN_B200_ACT_SIGMOID 10
+#define KUDNN_B200_ACT_GELU_TANH 20
+#define KUDNN_B200_ACT_SWISH 25
+#define KUDNN_B200_ACT_GELU_ERF 27
+
+/* Second-output operators.  EXT and IDENTICAL are KuDNN::ResOpsFunction::RES_EXT / RES_IDENTIAL
+ * (src/dnn/include/operations/kudnn_linear_res.hpp:25-29, arithmetic in src/dnn/src/kudnn_linear_res.cpp:57-122).
+ * The reference's RES_MUL is a second matrix product and is issued by the host as a second call.
+ * ELTWISE_MUL (out = c * res element-wise) has no counterpart in the reference. */
+#define KUDNN_B200_RES_NONE 0
+#define KUDNN_B200_RES_EXT 1
+#define KUDNN_B200_RES_IDENTICAL 2
+#define KUDNN_B200_RES_ELTWISE_MUL 3
+
+/* Kernel families, as reported by kudnn_b200_linear_last_kernel and accepted by ..._force_kernel. */
+#define KUDNN_B200_KERNEL_AUTO 0
+#define KUDNN_B200_KERNEL_SIMT 1     /* general strided FMA kernel: any layout, any size */
+#define KUDNN_B200_KERNEL_GEMV_FMA 2 /* m <= 4 streaming kernel, fp32 FMA + warp-shuffle reduction */
+#define KUDNN_B200_KERNEL_GEMV_MMA 3 /* m <= 16 streaming kernel, 16-bit inputs */
+#define KUDNN_B200_KERNEL_TC 4       /* tcgen05 / TMEM tensor-core kernel fed by TMA */
+
+/* Replaces the argument lists of the reference constructors:
+ *   Gemm(aInfo,bInfo,cInfo,biasInfo,numThreads)                     src/dnn/include/operations/kudnn_gemm.hpp:36-39
+ *   LinearActivationLayerFWD(a,b,c,bias,alpha,beta,kind,numThreads) .../kudnn_linear_activationlayer.hpp:44-52
+ *   LinearResFWD(a,b,c,bias,res,linearRes,alpha,beta,gamma,kind,..) .../kudnn_linear_res.hpp:50-59
+ * A TensorInfo (dims, type, layout, strides; src/dnn/include/types/kudnn_tensor_info.hpp:132-289) becomes a
+ * dtype code plus element strides of the logical dimensions; layouts are folded into the strides. */
+typedef struct kudnn_b200_linear_desc {
+    int64_t m, n, k;
+    int64_t batch[3]; /* leading batch extents, outermost first; 0 or 1 = absent */
+    int32_t a_dtype, b_dtype, c_dtype, bias_dtype, res_dtype, out_dtype;
+    int32_t has_bias, act, res_op, reserved;
+    float act_alpha, act_beta; /* activation parameters (relu slope, swish beta); not GEMM scalars */
+    int64_t a_sm, a_sk, a_sb[3];
+    int64_t b_sk, b_sn, b_sb[3];
+    int64_t c_sm, c_sn, c_sb[3];
+    int64_t bias_sm, bias_sn, bias_sb[3]; /* 0 = broadcast along that dimension */
+    int64_t res_sm, res_sn, res_sb[3];
+    int64_t out_sm, out_sn, out_sb[3];
+} kudnn_b200_linear_desc;
+
+/* Replaces the pointer/scalar arguments of the reference Run methods
+ * (kudnn_gemm.hpp:44-47, kudnn_linear_activationlayer.hpp:57-58, kudnn_linear_res.hpp:69-73). */
+typedef struct kudnn_b200_linear_args {
+    const void *a;
+    const void *b;
+    void *c;          /* may be NULL when res_op != NONE and only `out` is wanted */
+    const void *bias; /* non-NULL iff has_bias */
+    const void *res;  /* non-NULL iff res_op != NONE */
+    void *out;        /* non-NULL iff res_op != NONE */
+    float alpha, beta, gamma;
+} kudnn_b200_linear_args;
+
+typedef struct kudnn_b200_linear_s *kudnn_b200_linear_t;
+
+/* Host-only check of a descriptor; replaces the kernel-facing part of Gemm::ValidateInput
+ * (src/dnn/src/kudnn_gemm.cpp:384-476).  Touches no CUDA state. */
+KUDNN_B200_API int kudnn_b200_linear_validate(const kudnn_b200_linear_desc *desc);
+
+/* Primitive creation; replaces GemmImpl::GemmImpl (src/dnn/src/kudnn_gemm.cpp:830-857).  Host-only: device state is
+ * created on first use, on the device that is current at that time. */
+KUDNN_B200_API int kudnn_b200_linear_create(const kudnn_b200_linear_desc *desc, kudnn_b200_linear_t *handle);
+KUDNN_B200_API int kudnn_b200_linear_clone(kudnn_b200_linear_t src, kudnn_b200_linear_t *handle);
+KUDNN_B200_API int kudnn_b200_linear_destroy(kudnn_b200_linear_t handle);
+
+/* Pre-packs the weight operand `b` (host or device memory) into the layout the chosen kernel streams (K-major,
+ * 16-byte aligned rows; fp32 weights additionally split into TF32 hi/lo planes).  Later runs whose args->b equals
+ * `b` use the packed copy and do not read `b` again.  Replaces the per-call packing inside the reference's BLAS/JIT
+ * (src/dnn/src/matmul_jit/MatrixComputation/kudnn_default_impl_fp16fp16f32f32.cpp:929-962). */
+KUDNN_B200_API int kudnn_b200_linear_prepack(kudnn_b200_linear_t handle, const void *b, void *cuda_stream);
+
+/* Execute with DEVICE pointers on `cuda_stream` (a cudaStream_t, NULL = default stream); asynchronous.
+ * Replaces GemmImpl::Run / LinearActivationLayerFWDImpl::Run / LinearResFWDImpl::Run
+ * (src/dnn/src/kudnn_gemm.cpp:859-877, kudnn_linear_activationlayer.cpp:40-56, kudnn_linear_res.cpp:184-202). */
+KUDNN_B200_API int kudnn_b200_linear_run(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args,
+                                         void *cuda_stream);
+
+/* Execute with HOST pointers, as the reference's callers pass them: stages inputs to the device, runs, copies the
+ * outputs back and synchronises.  A weight pointer that was pre-packed is not copied again. */
+KUDNN_B200_API int kudnn_b200_linear_run_host(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args);
+
+/* Reads the device-side status word of the handle (bounded waits that gave up) after synchronising the stream. */
+KUDNN_B200_API int kudnn_b200_linear_check(kudnn_b200_linear_t handle, void *cuda_stream);
+
+/* Introspection used by tests and the benchmark. */
+KUDNN_B200_API int kudnn_b200_linear_force_kernel(kudnn_b200_linear_t handle, int kernel);
+KUDNN_B200_API int kudnn_b200_linear_last_kernel(kudnn_b200_linear_t handle);
+KUDNN_B200_API int kudnn_b200_linear_last_launches(kudnn_b200_linear_t handle);
+KUDNN_B200_API int64_t kudnn_b200_linear_workspace_bytes(kudnn_b200_linear_t handle);
+
+/* Row partition used by the sharded launchers: part `part` of `nparts` gets rows [*begin, *begin + *count),
+ * boundaries rounded to multiples of `align`.  Pure arithmetic. */
+KUDNN_B200_API int kudnn_b200_shard_range(int64_t total, int nparts, int part, int64_t align, int64_t *begin,
+                                          int64_t *count);
+
+KUDNN_B200_API const char *kudnn_b200_last_error(void);
+KUDNN_B200_API const char *kudnn_b200_version(void);
+KUDNN_B200_API int kudnn_b200_device_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* KUDNN_B200_H */

@@ -1,0 +1,570 @@
+// Streaming kernels for decode-shaped Linear (m <= 16): the weight matrix is read from HBM exactly once,
+// everything else stays on chip.  The reference reaches this shape through cblas_sgemv / cblas_bgemm
+// (src/dnn/src/kudnn_gemm.cpp:165-176, :222-226).
+//
+// Work decomposition (both kernels).  The weight matrix [n, k], K-contiguous, is cut into "blocks" of one
+// 16-byte load per lane.  All blocks are numbered row-major (unit by unit, k ascending inside a unit; a unit is a
+// weight row for the FMA kernel and a group of 8 weight rows for the MMA kernel) and the numbering is split into
+// equal contiguous spans, one per active warp, so every warp streams the same number of bytes no matter how n
+// relates to the SM count.  A warp whose span covers a unit completely finishes that unit on its own; a unit cut
+// by a span boundary is a split-K case: each warp involved stores its partial sums into its slot of the scratch
+// buffer, bumps the unit's arrival counter, and the warp that arrives last adds the slots in slot order (so the
+// result does not depend on timing) and runs the fused epilogue.  Counters return to zero before the kernel ends.
+//
+//   FMA kernel  m <= 4, fp32 / fp16 / bf16.  Lane l of a warp owns k = 8l..8l+7 (16-bit) of every block of a row,
+//               accumulates with fp32 FMA against the activations held in shared memory as fp32, and a
+//               warp-shuffle tree folds the 32 lanes when the row (or the span) ends.
+//   MMA kernel  m <= 16, fp16 / bf16.  A block is 8 rows x 32 k; the 16 bytes a lane loads feed two
+//               mma.sync.m16n8k16 (activations as the 16-row operand, zero padded), fp32 accumulators.  The
+//               contraction index inside a block is permuted identically for both operands so a lane's 16 bytes
+//               are consecutive in memory.  K is additionally cut into `ksplit` chunks across CTAs so the
+//               activation chunk fits shared memory.
+#include "kernels.cuh"
+
+#include <algorithm>
+#include <cstdlib>
+
+namespace kb {
+
+namespace {
+
+constexpr int kGemvThreads = 512;
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kMmaRowPadBytes = 64;  // keeps the 8 quarter-warp rows of an A-fragment load on distinct banks
+
+struct GemvParams {
+    const void *x;   // [m, k], K-contiguous, row pitch x_ld elements
+    const void *w;   // [n, k], K-contiguous, row pitch w_ld elements
+    long long x_ld, w_ld;
+    int m, n, k;
+    int kb;            // blocks per unit (per chunk for the MMA kernel)
+    int kc;            // chunk length in k (MMA kernel), multiple of 32
+    int ksplit;
+    int active_warps;  // per chunk
+    long long span;
+    long long total;   // blocks per chunk
+    int slots;         // slots per unit per chunk
+    float *partials;
+    unsigned int *counters;
+    EpiParams epi;
+};
+
+__device__ __forceinline__ uint4 ld_stream_16(const void *p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <int kDtype>
+__device__ __forceinline__ void unpack2(unsigned w, float &lo, float &hi)
+{
+    if (kDtype == KUDNN_B200_BF16) {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xffff0000u);
+    } else {
+        __half2 h = *reinterpret_cast<__half2 *>(&w);
+        float2 f = __half22float2(h);
+        lo = f.x;
+        hi = f.y;
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, off);
+    }
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------------ FMA kernel
+
+template <int kDtype, int kM, int kUnroll>
+__global__ void __launch_bounds__(kGemvThreads, (kUnroll <= 4) ? 2 : 1) gemv_fma_kernel(const GemvParams p)
+{
+    constexpr int kVec = (kDtype == KUDNN_B200_F32) ? 4 : 8;  // elements per 16-byte load
+    constexpr int kBlockK = 32 * kVec;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float *xs = reinterpret_cast<float *>(smem_raw);  // [kM][kpad]
+    const int kpad = p.kb * kBlockK;
+
+    for (int i = threadIdx.x; i < kM * kpad; i += kGemvThreads) {
+        const int mi = i / kpad, kk = i - mi * kpad;
+        float v = 0.0f;
+        if (kk < p.k) {
+            v = load_as_f32(p.x, kDtype, static_cast<long long>(mi) * p.x_ld + kk);
+        }
+        xs[i] = v;
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int warp = blockIdx.x * kGemvWarps + (threadIdx.x >> 5);
+    if (warp >= p.active_warps) {
+        return;
+    }
+    long long f = static_cast<long long>(warp) * p.span;
+    const long long f_end = (f + p.span < p.total) ? f + p.span : p.total;
+    const char *wbase = static_cast<const char *>(p.w);
+    const int esize = (kDtype == KUDNN_B200_F32) ? 4 : 2;
+
+    while (f < f_end) {
+        const long long row = f / p.kb;
+        const int kb0 = static_cast<int>(f - row * p.kb);
+        const int nb = static_cast<int>(((p.kb - kb0) < (f_end - f)) ? (p.kb - kb0) : (f_end - f));
+        const char *wrow = wbase + (row * p.w_ld + static_cast<long long>(lane) * kVec) * esize;
+
+        float acc[kM];
+#pragma unroll
+        for (int mi = 0; mi < kM; ++mi) {
+            acc[mi] = 0.0f;
+        }
+        for (int i = 0; i < nb; i += kUnroll) {
+            uint4 wv[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int kk = (kb0 + i + u) * kBlockK + lane * kVec;
+                wv[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (i + u < nb && kk < p.k) {
+                    wv[u] = ld_stream_16(wrow + static_cast<long long>(kb0 + i + u) * kBlockK * esize);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                if (i + u < nb) {
+                    const int kk = (kb0 + i + u) * kBlockK + lane * kVec;
+                    float wf[kVec];
+                    if (kDtype == KUDNN_B200_F32) {
+                        wf[0] = __uint_as_float(wv[u].x);
+                        wf[1] = __uint_as_float(wv[u].y);
+                        wf[2] = __uint_as_float(wv[u].z);
+                        wf[3] = __uint_as_float(wv[u].w);
+                    } else {
+                        unpack2<kDtype>(wv[u].x, wf[0], wf[1]);
+                        unpack2<kDtype>(wv[u].y, wf[2], wf[3]);
+                        unpack2<kDtype>(wv[u].z, wf[4 % kVec], wf[5 % kVec]);
+                        unpack2<kDtype>(wv[u].w, wf[6 % kVec], wf[7 % kVec]);
+                    }
+#pragma unroll
+                    for (int mi = 0; mi < kM; ++mi) {
+                        const float4 *xp = reinterpret_cast<const float4 *>(xs + mi * kpad + kk);
+#pragma unroll
+                        for (int q = 0; q < kVec / 4; ++q) {
+                            const float4 xv = xp[q];
+                            acc[mi] = fmaf(wf[q * 4 + 0], xv.x, acc[mi]);
+                            acc[mi] = fmaf(wf[q * 4 + 1], xv.y, acc[mi]);
+                            acc[mi] = fmaf(wf[q * 4 + 2], xv.z, acc[mi]);
+                            acc[mi] = fmaf(wf[q * 4 + 3], xv.w, acc[mi]);
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int mi = 0; mi < kM; ++mi) {
+            acc[mi] = warp_sum(acc[mi]);
+        }
+
+        const bool whole = (kb0 == 0) && (nb == p.kb);
+        if (whole) {
+            if (lane < kM) {
+                float v = acc[0];
+#pragma unroll
+                for (int mi = 1; mi < kM; ++mi) {
+                    v = (lane == mi) ? acc[mi] : v;
+                }
+                epilogue_scalar(p.epi, v, lane, row);
+            }
+        } else {
+            // split row: slot = position of this warp among the warps that touch the row
+            const long long first_blk = row * p.kb;
+            const int w0 = static_cast<int>(first_blk / p.span);
+            const int w1 = static_cast<int>((first_blk + p.kb - 1) / p.span);
+            const int pieces = w1 - w0 + 1;
+            const int slot = warp - w0;
+            float *mine = p.partials + (row * p.slots + slot) * kM;
+            if (lane == 0) {
+#pragma unroll
+                for (int mi = 0; mi < kM; ++mi) {
+                    mine[mi] = acc[mi];
+                }
+                __threadfence();
+                const unsigned old = atomicAdd(p.counters + row, 1u);
+                if (old == static_cast<unsigned>(pieces - 1)) {
+                    __threadfence();
+                    const float *all = p.partials + row * p.slots * kM;
+#pragma unroll
+                    for (int mi = 0; mi < kM; ++mi) {
+                        float s = 0.0f;
+                        for (int j = 0; j < pieces; ++j) {
+                            s += __ldcg(all + j * kM + mi);
+                        }
+                        epilogue_scalar(p.epi, s, mi, row);
+                    }
+                    p.counters[row] = 0u;
+                }
+            }
+            __syncwarp();
+        }
+        f += nb;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ MMA kernel
+
+template <int kDtype>
+__device__ __forceinline__ void mma_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                          unsigned b0, unsigned b1)
+{
+    if (kDtype == KUDNN_B200_BF16) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// kRows16: activations occupy both 8-row halves of the 16-row operand (m > 8)
+template <int kDtype, bool kRows16, int kUnroll>
+__global__ void __launch_bounds__(kGemvThreads, (kUnroll <= 4) ? 2 : 1) gemv_mma_kernel(const GemvParams p)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int kRows = kRows16 ? 16 : 8;
+    const int row_bytes = p.kc * 2 + kMmaRowPadBytes;
+    const int chunk = blockIdx.x % p.ksplit;
+    const int cta_in_chunk = blockIdx.x / p.ksplit;
+    const int kc0 = chunk * p.kc;
+
+    // activations of this chunk -> shared memory (16-bit, zero padded in m and k)
+    {
+        const int vec_per_row = p.kc / 8;
+        const unsigned short *xg = static_cast<const unsigned short *>(p.x);
+        for (int i = threadIdx.x; i < kRows * vec_per_row; i += kGemvThreads) {
+            const int mi = i / vec_per_row, v = i - mi * vec_per_row;
+            const int kk = kc0 + v * 8;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (mi < p.m && kk < p.k) {
+                val = *reinterpret_cast<const uint4 *>(xg + static_cast<long long>(mi) * p.x_ld + kk);
+            }
+            *reinterpret_cast<uint4 *>(smem_raw + mi * row_bytes + v * 16) = val;
+        }
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int warp = cta_in_chunk * kGemvWarps + (threadIdx.x >> 5);
+    if (warp >= p.active_warps) {
+        return;
+    }
+    long long f = static_cast<long long>(warp) * p.span;
+    const long long f_end = (f + p.span < p.total) ? f + p.span : p.total;
+    const unsigned short *wg = static_cast<const unsigned short *>(p.w);
+    const unsigned char *xa_row = smem_raw + gid * row_bytes + tig * 16;
+    const unsigned char *xb_row = smem_raw + (gid + 8) * row_bytes + tig * 16;
+
+    while (f < f_end) {
+        const long long group = f / p.kb;
+        const int kb0 = static_cast<int>(f - group * p.kb);
+        const int nb = static_cast<int>(((p.kb - kb0) < (f_end - f)) ? (p.kb - kb0) : (f_end - f));
+        const long long wrow_idx = group * 8 + gid;
+        const bool row_ok = wrow_idx < p.n;
+        const unsigned short *wrow = wg + wrow_idx * p.w_ld + kc0 + tig * 8;
+
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int i = 0; i < nb; i += kUnroll) {
+            uint4 wv[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int kloc = (kb0 + i + u) * 32;
+                wv[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (i + u < nb && row_ok && (kc0 + kloc + tig * 8) < p.k) {
+                    wv[u] = ld_stream_16(wrow + kloc);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                if (i + u < nb) {
+                    const int kloc = (kb0 + i + u) * 32;
+                    const uint4 xa = *reinterpret_cast<const uint4 *>(xa_row + kloc * 2);
+                    uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+                    if (kRows16) {
+                        xb = *reinterpret_cast<const uint4 *>(xb_row + kloc * 2);
+                    }
+                    mma_16816<kDtype>(acc, xa.x, xb.x, xa.y, xb.y, wv[u].x, wv[u].y);
+                    mma_16816<kDtype>(acc, xa.z, xb.z, xa.w, xb.w, wv[u].z, wv[u].w);
+                }
+            }
+        }
+
+        // lane holds y[gid][n0 + 2*tig + {0,1}] in acc[0..1] and y[gid + 8][...] in acc[2..3]
+        const long long n0 = group * 8 + tig * 2;
+        const long long first_blk = group * p.kb;
+        const int w0 = static_cast<int>(first_blk / p.span);
+        const int w1 = static_cast<int>((first_blk + p.kb - 1) / p.span);
+        const int pieces = w1 - w0 + 1;
+        const bool whole = (p.ksplit == 1) && (pieces == 1);
+        bool finish = whole;
+        if (!whole) {
+            const int slot = chunk * p.slots + (warp - w0);
+            float *unit = p.partials + group * (static_cast<long long>(p.ksplit) * p.slots * 128);
+            *reinterpret_cast<float4 *>(unit + slot * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            __threadfence();
+            __syncwarp();
+            unsigned old = 0u;
+            if (lane == 0) {
+                old = atomicAdd(p.counters + group, 1u);
+            }
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == static_cast<unsigned>(p.ksplit * pieces - 1)) {
+                __threadfence();
+                float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                for (int c = 0; c < p.ksplit; ++c) {
+                    for (int j = 0; j < pieces; ++j) {
+                        const float4 v =
+                            __ldcg(reinterpret_cast<const float4 *>(unit + (c * p.slots + j) * 128 + lane * 4));
+                        s[0] += v.x;
+                        s[1] += v.y;
+                        s[2] += v.z;
+                        s[3] += v.w;
+                    }
+                }
+                acc[0] = s[0];
+                acc[1] = s[1];
+                acc[2] = s[2];
+                acc[3] = s[3];
+                finish = true;
+                if (lane == 0) {
+                    p.counters[group] = 0u;
+                }
+            }
+        }
+        if (finish) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int mi = gid + ((e >= 2) ? 8 : 0);
+                const long long ni = n0 + (e & 1);
+                if (mi < p.m && ni < p.n) {
+                    epilogue_scalar(p.epi, acc[e], mi, ni);
+                }
+            }
+        }
+        f += nb;
+    }
+}
+
+int env_int(const char *name, int fallback)
+{
+    const char *v = std::getenv(name);
+    if (v == nullptr || *v == '\0') {
+        return fallback;
+    }
+    return std::atoi(v);
+}
+
+template <typename K>
+cudaError_t set_smem(K kernel, size_t bytes)
+{
+    if (bytes > 48 * 1024) {
+        return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    }
+    return cudaSuccess;
+}
+
+template <int kDtype, int kUnroll>
+cudaError_t launch_fma_m(const GemvParams &p, const GemvPlan &plan, cudaStream_t stream)
+{
+#define KB_FMA_CASE(M)                                                                                     \
+    case M: {                                                                                              \
+        cudaError_t e = set_smem(gemv_fma_kernel<kDtype, M, kUnroll>, plan.smem_bytes);                    \
+        if (e != cudaSuccess) return e;                                                                    \
+        gemv_fma_kernel<kDtype, M, kUnroll><<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);        \
+        break;                                                                                             \
+    }
+    switch (p.m) {
+        KB_FMA_CASE(1)
+        KB_FMA_CASE(2)
+        KB_FMA_CASE(3)
+        KB_FMA_CASE(4)
+        default:
+            return cudaErrorInvalidValue;
+    }
+#undef KB_FMA_CASE
+    return cudaGetLastError();
+}
+
+template <int kDtype, int kUnroll>
+cudaError_t launch_mma_rows(const GemvParams &p, const GemvPlan &plan, cudaStream_t stream)
+{
+    if (p.m > 8) {
+        cudaError_t e = set_smem(gemv_mma_kernel<kDtype, true, kUnroll>, plan.smem_bytes);
+        if (e != cudaSuccess) return e;
+        gemv_mma_kernel<kDtype, true, kUnroll><<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);
+    } else {
+        cudaError_t e = set_smem(gemv_mma_kernel<kDtype, false, kUnroll>, plan.smem_bytes);
+        if (e != cudaSuccess) return e;
+        gemv_mma_kernel<kDtype, false, kUnroll><<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// Decides whether a problem can take a streaming kernel and how it is cut.  Pure host arithmetic.
+bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPlan *plan)
+{
+    if (pr.batch_count != 1 || pr.m > 16 || pr.m < 1) {
+        return false;
+    }
+    if (pr.a_dtype != pr.b_dtype || pr.a_sk != 1 || pr.b_sk != 1) {
+        return false;
+    }
+    const int dt = pr.a_dtype;
+    const int vec = (dt == KUDNN_B200_F32) ? 4 : 8;
+    const int esize = dtype_size(dt);
+    if (pr.k % vec != 0 || pr.a_sm % vec != 0 || pr.b_sn % vec != 0 || pr.k > (1 << 24) || pr.n > (1 << 28)) {
+        return false;
+    }
+    if ((reinterpret_cast<uintptr_t>(pr.a) & 15u) != 0 || (reinterpret_cast<uintptr_t>(pr.b) & 15u) != 0) {
+        return false;
+    }
+    (void)esize;
+    const int max_smem = 200 * 1024;
+    int kernel = forced_kernel;
+    if (kernel != KUDNN_B200_KERNEL_GEMV_FMA && kernel != KUDNN_B200_KERNEL_GEMV_MMA) {
+        const int fma_max_m = env_int("KUDNN_B200_GEMV_FMA_MAX_M", 2);
+        kernel = (dt == KUDNN_B200_F32 || pr.m <= fma_max_m) ? KUDNN_B200_KERNEL_GEMV_FMA : KUDNN_B200_KERNEL_GEMV_MMA;
+    }
+    plan->kernel = kernel;
+    plan->block = kGemvThreads;
+    if (kernel == KUDNN_B200_KERNEL_GEMV_FMA) {
+        if (pr.m > 4) {
+            return false;
+        }
+        const int block_k = 32 * vec;
+        const long long kb = (pr.k + block_k - 1) / block_k;
+        const size_t smem = static_cast<size_t>(pr.m) * kb * block_k * sizeof(float);
+        if (smem > static_cast<size_t>(max_smem)) {
+            return false;
+        }
+        const int ctas_per_sm = (smem <= 100 * 1024) ? 2 : 1;
+        const int grid = sm_count * ctas_per_sm;
+        const long long total = pr.n * kb;
+        long long active = std::min<long long>(static_cast<long long>(grid) * kGemvWarps, pr.n);  // span >= kb
+        active = std::max<long long>(active, 1);
+        const long long span = (total + active - 1) / active;
+        active = (total + span - 1) / span;
+        plan->grid = static_cast<int>((active + kGemvWarps - 1) / kGemvWarps);
+        plan->ksplit = 1;
+        plan->active_warps = static_cast<int>(active);
+        plan->span = span;
+        plan->slots = 2;
+        plan->smem_bytes = smem;
+        plan->partial_floats = pr.n * 2 * pr.m;
+        plan->counter_count = pr.n;
+        return true;
+    }
+    // MMA kernel
+    if (dt == KUDNN_B200_F32) {
+        return false;
+    }
+    const int rows = pr.m > 8 ? 16 : 8;
+    int ksplit = env_int("KUDNN_B200_GEMV_KSPLIT", 0);
+    if (ksplit <= 0) {
+        ksplit = 1;
+        while (ksplit < 64) {
+            const long long kc = ((pr.k + ksplit - 1) / ksplit + 31) / 32 * 32;
+            if (static_cast<size_t>(rows) * (kc * 2 + kMmaRowPadBytes) <= 100 * 1024) {
+                break;
+            }
+            ksplit *= 2;
+        }
+    }
+    const long long kc = ((pr.k + ksplit - 1) / ksplit + 31) / 32 * 32;
+    const size_t smem = static_cast<size_t>(rows) * (kc * 2 + kMmaRowPadBytes);
+    if (smem > static_cast<size_t>(max_smem)) {
+        return false;
+    }
+    const int ctas_per_sm = (smem <= 100 * 1024) ? 2 : 1;
+    int grid = sm_count * ctas_per_sm;
+    grid = std::max(grid / ksplit, 1) * ksplit;
+    const long long groups = (pr.n + 7) / 8;
+    const long long kbc = kc / 32;
+    const long long total = groups * kbc;
+    long long active = std::min<long long>(static_cast<long long>(grid / ksplit) * kGemvWarps, 2 * groups);
+    active = std::max<long long>(active, 1);
+    const long long span = (total + active - 1) / active;
+    active = (total + span - 1) / span;
+    plan->grid = static_cast<int>((active + kGemvWarps - 1) / kGemvWarps) * ksplit;
+    plan->ksplit = ksplit;
+    plan->active_warps = static_cast<int>(active);
+    plan->span = span;
+    plan->slots = static_cast<int>((kbc + span - 1) / span) + 1;
+    plan->smem_bytes = smem;
+    plan->partial_floats = groups * ksplit * plan->slots * 128;
+    plan->counter_count = groups;
+    return true;
+}
+
+cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const GemvWorkspace &ws, cudaStream_t stream)
+{
+    if (ws.partial_floats < plan.partial_floats || ws.counter_count < plan.counter_count) {
+        return cudaErrorInvalidValue;
+    }
+    GemvParams p;
+    p.x = pr.a;
+    p.w = pr.b;
+    p.x_ld = pr.a_sm;
+    p.w_ld = pr.b_sn;
+    p.m = static_cast<int>(pr.m);
+    p.n = static_cast<int>(pr.n);
+    p.k = static_cast<int>(pr.k);
+    p.ksplit = plan.ksplit;
+    p.active_warps = plan.active_warps;
+    p.span = plan.span;
+    p.slots = plan.slots;
+    p.partials = ws.partials;
+    p.counters = ws.counters;
+    p.epi = pr.epi;
+    const int dt = pr.a_dtype;
+    const int unroll = env_int("KUDNN_B200_GEMV_UNROLL", 4);
+    if (plan.kernel == KUDNN_B200_KERNEL_GEMV_FMA) {
+        const int vec = (dt == KUDNN_B200_F32) ? 4 : 8;
+        p.kb = static_cast<int>((pr.k + 32 * vec - 1) / (32 * vec));
+        p.kc = 0;
+        p.total = pr.n * p.kb;
+        if (dt == KUDNN_B200_F32) {
+            return unroll >= 8 ? launch_fma_m<KUDNN_B200_F32, 8>(p, plan, stream)
+                               : launch_fma_m<KUDNN_B200_F32, 4>(p, plan, stream);
+        }
+        if (dt == KUDNN_B200_F16) {
+            return unroll >= 8 ? launch_fma_m<KUDNN_B200_F16, 8>(p, plan, stream)
+                               : launch_fma_m<KUDNN_B200_F16, 4>(p, plan, stream);
+        }
+        return unroll >= 8 ? launch_fma_m<KUDNN_B200_BF16, 8>(p, plan, stream)
+                           : launch_fma_m<KUDNN_B200_BF16, 4>(p, plan, stream);
+    }
+    const long long kc = ((pr.k + plan.ksplit - 1) / plan.ksplit + 31) / 32 * 32;
+    p.kc = static_cast<int>(kc);
+    p.kb = static_cast<int>(kc / 32);
+    p.total = ((pr.n + 7) / 8) * p.kb;
+    if (dt == KUDNN_B200_F16) {
+        return unroll >= 8 ? launch_mma_rows<KUDNN_B200_F16, 8>(p, plan, stream)
+                           : launch_mma_rows<KUDNN_B200_F16, 4>(p, plan, stream);
+    }
+    return unroll >= 8 ? launch_mma_rows<KUDNN_B200_BF16, 8>(p, plan, stream)
+                       : launch_mma_rows<KUDNN_B200_BF16, 4>(p, plan, stream);
+}
+
+}  // namespace kb

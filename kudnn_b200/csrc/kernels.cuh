@@ -1,0 +1,78 @@
+// Launch interface between the C-ABI dispatcher and the kernel families.
+#pragma once
+
+#include "common.cuh"
+
+namespace kb {
+
+// One resolved problem: device pointers, element strides, epilogue, batch.
+struct LinearProblem {
+    const void *a;
+    const void *b;
+    long long m, n, k;
+    long long a_sm, a_sk, b_sk, b_sn;
+    int a_dtype, b_dtype;
+    EpiParams epi;
+    BatchParams batch;
+    long long batch_count;
+};
+
+// Scratch for the streaming kernels' cross-warp reduction (device memory owned by the handle).
+struct GemvWorkspace {
+    float *partials;         // slots of partial sums
+    unsigned int *counters;  // one arrival counter per row (FMA kernel) or per 8-row group (MMA kernel); zero at rest
+    long long partial_floats;
+    long long counter_count;
+};
+
+struct GemvPlan {
+    int kernel;         // KUDNN_B200_KERNEL_GEMV_FMA / _MMA
+    int grid, block;    // launch shape
+    int ksplit;         // K chunks (MMA kernel)
+    int active_warps;   // warps that take a span of the flattened work
+    long long span;     // work blocks per active warp
+    int slots;          // partial slots per row / row group
+    size_t smem_bytes;
+    long long partial_floats, counter_count;
+};
+
+cudaError_t launch_simt(const LinearProblem &pr, cudaStream_t stream);
+
+// Streaming kernels for m <= 16 (2-D problems, K-contiguous operands).
+bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPlan *plan);
+cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const GemvWorkspace &ws, cudaStream_t stream);
+
+// Tensor-core kernel.  Operands must be K-major with 16-byte aligned rows; see tc_eligible().
+struct TcOperands {
+    const void *a;  // [m, k_total] K-major
+    const void *b;  // [n, k_total] K-major
+    long long lda, ldb;   // row pitch in elements
+    long long k_total;    // contraction length as laid out (3*k for the split-fp32 form)
+    int kind;             // KUDNN_B200_F16 / _BF16 / _F32 (tf32 planes)
+};
+struct TcPlan {
+    int block_n;   // 128 or 256
+    int stages;
+    int grid;
+    size_t smem_bytes;
+    unsigned char tmap_a[128] __attribute__((aligned(64)));
+    unsigned char tmap_b[128] __attribute__((aligned(64)));
+};
+bool tc_available();
+const char *tc_unavailable_reason();
+cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm_count, TcPlan *plan);
+cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams &epi, long long m, long long n,
+                      DeviceStatus *status, cudaStream_t stream);
+
+// Packing / conversion kernels.
+// dst[r, kk] (row pitch ldd, K-major) = src[r*s_row + kk*s_k] converted to dst_dtype; columns [k, k_pad) are zeroed.
+cudaError_t launch_pack_kmajor(const void *src, int src_dtype, long long rows, long long k, long long s_row,
+                               long long s_k, void *dst, int dst_dtype, long long ldd, long long k_pad,
+                               cudaStream_t stream);
+// fp32 -> three K-major TF32 planes side by side at the start of each dst row (row pitch ldd floats).  With
+// hi = tf32(x) and lo = tf32(x - hi), activations are laid out [lo | hi | hi] and weights [hi | lo | hi], so that one
+// contraction over the 3 * k_pad columns yields a_lo.b_hi + a_hi.b_lo + a_hi.b_hi.
+cudaError_t launch_split_tf32(const void *src, long long rows, long long k, long long s_row, long long s_k, float *dst,
+                              long long ldd, long long k_pad, int is_weight, cudaStream_t stream);
+
+}  // namespace kb

@@ -1,0 +1,852 @@
+// C-ABI of the Linear(+post-op) path: descriptor validation, handle life cycle, weight pre-packing, kernel
+// selection and launch, host-pointer staging.  The entry points are declared in include/kudnn_b200.h.
+#include "kernels.cuh"
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    std::vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int fail_cuda(cudaError_t e, const char *what)
+{
+    (void)cudaGetLastError();
+    if (e == cudaErrorMemoryAllocation) {
+        return fail(KUDNN_B200_ALLOC_FAILED, "%s: device allocation failed", what);
+    }
+    return fail(KUDNN_B200_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool is_float_dtype(int dt)
+{
+    return dt == KUDNN_B200_F32 || dt == KUDNN_B200_F16 || dt == KUDNN_B200_BF16;
+}
+
+long long batch_extent(const kudnn_b200_linear_desc &d, int i)
+{
+    return d.batch[i] > 0 ? d.batch[i] : 1;
+}
+
+// number of elements spanned by a tensor with the given extents and strides
+long long span_elems(long long e0, long long s0, long long e1, long long s1, const kudnn_b200_linear_desc &d,
+                     const int64_t sb[3])
+{
+    long long last = (e0 - 1) * s0 + (e1 - 1) * s1;
+    for (int i = 0; i < 3; ++i) {
+        last += (batch_extent(d, i) - 1) * sb[i];
+    }
+    return last + 1;
+}
+
+struct DeviceBuffer {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    cudaError_t reserve(size_t need)
+    {
+        if (need <= bytes) {
+            return cudaSuccess;
+        }
+        if (ptr != nullptr) {
+            cudaFree(ptr);
+            ptr = nullptr;
+            bytes = 0;
+        }
+        cudaError_t e = cudaMalloc(&ptr, need);
+        if (e == cudaSuccess) {
+            bytes = need;
+        }
+        return e;
+    }
+    void release()
+    {
+        if (ptr != nullptr) {
+            cudaFree(ptr);
+        }
+        ptr = nullptr;
+        bytes = 0;
+    }
+};
+
+}  // namespace
+
+struct kudnn_b200_linear_s {
+    kudnn_b200_linear_desc d;
+    int forced_kernel = KUDNN_B200_KERNEL_AUTO;
+    int last_kernel = 0;
+    int last_launches = 0;
+    int device = -1;
+    int sm_count = 0;
+    std::mutex lock;
+
+    DeviceBuffer status;        // kb::DeviceStatus
+    DeviceBuffer gemv_partials, gemv_counters;
+    DeviceBuffer a_scratch;     // per-call packed activations
+    DeviceBuffer b_scratch;     // per-call packed weights (when not pre-packed)
+    DeviceBuffer b_packed;      // pre-packed weights
+    DeviceBuffer stage[6];      // host-pointer staging: a, b, c, bias, res, out
+
+    // pre-pack state
+    const void *packed_key = nullptr;  // the caller's weight pointer the packed copy stands for
+    const void *packed_ptr = nullptr;  // what the tensor-core kernel reads (b_packed.ptr, or the caller's device
+                                       // pointer when that already is K-major); fp32: the three TF32 planes
+    const void *packed_raw = nullptr;  // K-major copy in the original element type (what the other kernels read)
+    long long packed_ld = 0, packed_ktotal = 0;
+
+    // tensor-map cache of the last tensor-core launch
+    kb::TcPlan tc_plan;
+    const void *plan_a = nullptr, *plan_b = nullptr;
+    bool plan_valid = false;
+};
+
+namespace {
+
+using Handle = kudnn_b200_linear_s;
+
+int ensure_device(Handle *h)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(KUDNN_B200_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    }
+    if (h->device == dev) {
+        return KUDNN_B200_OK;
+    }
+    if (h->device != -1) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "handle was first used on device %d, current device is %d", h->device, dev);
+    }
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "cudaGetDeviceProperties");
+    }
+    if (prop.major != 10) {
+        return fail(KUDNN_B200_NO_DEVICE, "device %d is sm_%d%d; this library carries sm_100a code only", dev, prop.major,
+                    prop.minor);
+    }
+    e = h->status.reserve(sizeof(kb::DeviceStatus));
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "status block");
+    }
+    e = cudaMemset(h->status.ptr, 0, sizeof(kb::DeviceStatus));
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "status block");
+    }
+    h->device = dev;
+    h->sm_count = prop.multiProcessorCount;
+    return KUDNN_B200_OK;
+}
+
+void fill_epi(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, kb::EpiParams *e)
+{
+    e->c = a.c;
+    e->bias = a.bias;
+    e->res = a.res;
+    e->out = a.out;
+    e->c_sm = d.c_sm;
+    e->c_sn = d.c_sn;
+    e->bias_sm = d.bias_sm;
+    e->bias_sn = d.bias_sn;
+    e->res_sm = d.res_sm;
+    e->res_sn = d.res_sn;
+    e->out_sm = d.out_sm;
+    e->out_sn = d.out_sn;
+    e->alpha = a.alpha;
+    e->beta = a.beta;
+    e->gamma = a.gamma;
+    e->act_alpha = d.act_alpha;
+    e->c_dtype = d.c_dtype;
+    e->bias_dtype = d.bias_dtype;
+    e->res_dtype = d.res_dtype;
+    e->out_dtype = d.out_dtype;
+    e->has_bias = d.has_bias;
+    e->act = d.act;
+    e->res_op = d.res_op;
+    e->m = static_cast<int>(d.m);
+    e->n = static_cast<int>(d.n);
+}
+
+void fill_problem(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, kb::LinearProblem *p)
+{
+    p->a = a.a;
+    p->b = a.b;
+    p->m = d.m;
+    p->n = d.n;
+    p->k = d.k;
+    p->a_sm = d.a_sm;
+    p->a_sk = d.a_sk;
+    p->b_sk = d.b_sk;
+    p->b_sn = d.b_sn;
+    p->a_dtype = d.a_dtype;
+    p->b_dtype = d.b_dtype;
+    fill_epi(d, a, &p->epi);
+    p->batch.n1 = batch_extent(d, 1);
+    p->batch.n2 = batch_extent(d, 2);
+    for (int i = 0; i < 3; ++i) {
+        p->batch.a_sb[i] = d.a_sb[i];
+        p->batch.b_sb[i] = d.b_sb[i];
+        p->batch.c_sb[i] = d.c_sb[i];
+        p->batch.bias_sb[i] = d.bias_sb[i];
+        p->batch.res_sb[i] = d.res_sb[i];
+        p->batch.out_sb[i] = d.out_sb[i];
+    }
+    p->batch_count = batch_extent(d, 0) * batch_extent(d, 1) * batch_extent(d, 2);
+}
+
+bool aligned16(const void *p)
+{
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+// K-major with rows that start on 16-byte boundaries: usable by TMA and by the streaming kernels as is
+bool kmajor_ready(const void *p, int dtype, long long s_row, long long s_k, long long rows)
+{
+    const int vec = 16 / kb::dtype_size(dtype);
+    return s_k == 1 && aligned16(p) && (rows == 1 || s_row % vec == 0);
+}
+
+long long round_up(long long v, long long a)
+{
+    return (v + a - 1) / a * a;
+}
+
+// Packs the weight operand into `buf`.  16-bit: [n, k_pad] K-major.  fp32: rows of [hi | lo | hi | raw] planes
+// (raw only when with_raw), each k_pad floats; the tensor-core kernel contracts over the first three.
+int pack_weights(Handle *h, const void *b_dev, DeviceBuffer *buf, bool with_raw, cudaStream_t stream, long long *ld,
+                 long long *ktotal, const void **raw, int *launches)
+{
+    const kudnn_b200_linear_desc &d = h->d;
+    if (d.b_dtype == KUDNN_B200_F32) {
+        const long long k_pad = round_up(d.k, 32);
+        const long long pitch = (with_raw ? 4 : 3) * k_pad;
+        cudaError_t e = buf->reserve(static_cast<size_t>(d.n) * pitch * sizeof(float));
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "packed weights");
+        }
+        float *base = static_cast<float *>(buf->ptr);
+        e = kb::launch_split_tf32(b_dev, d.n, d.k, d.b_sn, d.b_sk, base, pitch, k_pad, 1, stream);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "weight split kernel");
+        }
+        *launches += 1;
+        *raw = nullptr;
+        if (with_raw) {
+            e = kb::launch_pack_kmajor(b_dev, KUDNN_B200_F32, d.n, d.k, d.b_sn, d.b_sk, base + 3 * k_pad, KUDNN_B200_F32,
+                                       pitch, k_pad, stream);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "weight pack kernel");
+            }
+            *launches += 1;
+            *raw = base + 3 * k_pad;
+        }
+        *ld = pitch;
+        *ktotal = 3 * k_pad;
+    } else {
+        const long long k_pad = round_up(d.k, 8);
+        cudaError_t e = buf->reserve(static_cast<size_t>(d.n) * k_pad * 2);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "packed weights");
+        }
+        e = kb::launch_pack_kmajor(b_dev, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, buf->ptr, d.b_dtype, k_pad, k_pad, stream);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "weight pack kernel");
+        }
+        *launches += 1;
+        *ld = k_pad;
+        *ktotal = d.k;
+        *raw = buf->ptr;
+    }
+    return KUDNN_B200_OK;
+}
+
+int run_device(Handle *h, const kudnn_b200_linear_args &args, cudaStream_t stream)
+{
+    const kudnn_b200_linear_desc &d = h->d;
+    if (args.a == nullptr || args.b == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run: a and b must not be null");
+    }
+    if ((d.has_bias != 0) != (args.bias != nullptr)) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run: bias pointer does not match the descriptor");
+    }
+    if (d.res_op != KUDNN_B200_RES_NONE) {
+        if (args.res == nullptr || args.out == nullptr) {
+            return fail(KUDNN_B200_BAD_ARGUMENTS, "run: res and out must not be null for this descriptor");
+        }
+    } else if (args.c == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run: c must not be null");
+    }
+    if (args.beta != 0.0f && args.c == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run: beta != 0 needs c");
+    }
+    int rc = ensure_device(h);
+    if (rc != KUDNN_B200_OK) {
+        return rc;
+    }
+
+    kb::LinearProblem pr;
+    fill_problem(d, args, &pr);
+    int launches = 0;
+    const int forced = h->forced_kernel;
+    const bool use_packed = (h->packed_key != nullptr && h->packed_key == args.b);
+    const bool two_d = pr.batch_count == 1;
+    if (use_packed) {
+        // every kernel reads the packed copy; the caller's pointer (possibly host memory) is only the key
+        pr.b = h->packed_raw;
+        pr.b_sk = 1;
+        pr.b_sn = h->packed_ld;
+    }
+
+    // ---- streaming kernels (m <= 16)
+    if (two_d && d.m <= 16 &&
+        (forced == KUDNN_B200_KERNEL_AUTO || forced == KUDNN_B200_KERNEL_GEMV_FMA || forced == KUDNN_B200_KERNEL_GEMV_MMA)) {
+        const kb::LinearProblem &gp = pr;
+        kb::GemvPlan plan;
+        if (kb::gemv_plan(gp, h->sm_count, forced, &plan)) {
+            cudaError_t e = cudaSuccess;
+            if (h->gemv_partials.bytes < static_cast<size_t>(plan.partial_floats) * sizeof(float)) {
+                e = h->gemv_partials.reserve(static_cast<size_t>(plan.partial_floats) * sizeof(float));
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "streaming-kernel scratch");
+                }
+            }
+            if (h->gemv_counters.bytes < static_cast<size_t>(plan.counter_count) * sizeof(unsigned)) {
+                e = h->gemv_counters.reserve(static_cast<size_t>(plan.counter_count) * sizeof(unsigned));
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "streaming-kernel counters");
+                }
+                e = cudaMemsetAsync(h->gemv_counters.ptr, 0, h->gemv_counters.bytes, stream);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "streaming-kernel counters");
+                }
+            }
+            kb::GemvWorkspace ws;
+            ws.partials = static_cast<float *>(h->gemv_partials.ptr);
+            ws.counters = static_cast<unsigned *>(h->gemv_counters.ptr);
+            ws.partial_floats = static_cast<long long>(h->gemv_partials.bytes / sizeof(float));
+            ws.counter_count = static_cast<long long>(h->gemv_counters.bytes / sizeof(unsigned));
+            e = kb::launch_gemv(gp, plan, ws, stream);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "streaming kernel launch");
+            }
+            h->last_kernel = plan.kernel;
+            h->last_launches = 1;
+            return KUDNN_B200_OK;
+        }
+        if (forced != KUDNN_B200_KERNEL_AUTO) {
+            return fail(KUDNN_B200_UNSUPPORTED, "the forced streaming kernel cannot take this problem");
+        }
+    }
+
+    // ---- tensor-core kernel
+    const bool tc_types = d.a_dtype == d.b_dtype;
+    const bool tc_worth = static_cast<double>(d.m) * d.n * d.k >= 1.0e6 * 8 && d.k >= 32;
+    if (two_d && tc_types && (forced == KUDNN_B200_KERNEL_TC || (forced == KUDNN_B200_KERNEL_AUTO && tc_worth))) {
+        if (!kb::tc_available()) {
+            if (forced == KUDNN_B200_KERNEL_TC) {
+                return fail(KUDNN_B200_UNSUPPORTED, "tensor-core kernel unavailable: %s", kb::tc_unavailable_reason());
+            }
+        } else {
+            kb::TcOperands ops;
+            ops.kind = d.a_dtype;
+            const bool f32 = d.a_dtype == KUDNN_B200_F32;
+            // weights
+            if (use_packed) {
+                ops.b = h->packed_ptr;
+                ops.ldb = h->packed_ld;
+                ops.k_total = h->packed_ktotal;
+            } else if (!f32 && kmajor_ready(args.b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
+                ops.b = args.b;
+                ops.ldb = d.b_sn;
+                ops.k_total = d.k;
+            } else {
+                long long ld = 0, kt = 0;
+                const void *raw = nullptr;
+                rc = pack_weights(h, args.b, &h->b_scratch, false, stream, &ld, &kt, &raw, &launches);
+                if (rc != KUDNN_B200_OK) {
+                    return rc;
+                }
+                ops.b = h->b_scratch.ptr;
+                ops.ldb = ld;
+                ops.k_total = kt;
+            }
+            // activations
+            if (f32) {
+                const long long k_pad = round_up(d.k, 32);
+                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * 3 * k_pad * sizeof(float));
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "activation planes");
+                }
+                e = kb::launch_split_tf32(args.a, d.m, d.k, d.a_sm, d.a_sk, static_cast<float *>(h->a_scratch.ptr), 3 * k_pad,
+                                          k_pad, 0, stream);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "activation split kernel");
+                }
+                launches += 1;
+                ops.a = h->a_scratch.ptr;
+                ops.lda = 3 * k_pad;
+            } else if (kmajor_ready(args.a, d.a_dtype, d.a_sm, d.a_sk, d.m)) {
+                ops.a = args.a;
+                ops.lda = d.a_sm;
+            } else {
+                const long long k_pad = round_up(d.k, 8);
+                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * k_pad * 2);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "packed activations");
+                }
+                e = kb::launch_pack_kmajor(args.a, d.a_dtype, d.m, d.k, d.a_sm, d.a_sk, h->a_scratch.ptr, d.a_dtype, k_pad,
+                                           k_pad, stream);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "activation pack kernel");
+                }
+                launches += 1;
+                ops.a = h->a_scratch.ptr;
+                ops.lda = k_pad;
+            }
+            if (!(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b)) {
+                cudaError_t e = kb::tc_make_plan(ops, d.m, d.n, h->sm_count, &h->tc_plan);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "tensor map encoding");
+                }
+                h->plan_a = ops.a;
+                h->plan_b = ops.b;
+                h->plan_valid = true;
+            }
+            cudaError_t e = kb::launch_tc(ops, h->tc_plan, pr.epi, d.m, d.n,
+                                          static_cast<kb::DeviceStatus *>(h->status.ptr), stream);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "tensor-core kernel launch");
+            }
+            h->last_kernel = KUDNN_B200_KERNEL_TC;
+            h->last_launches = launches + 1;
+            return KUDNN_B200_OK;
+        }
+    } else if (forced == KUDNN_B200_KERNEL_TC) {
+        return fail(KUDNN_B200_UNSUPPORTED, "the tensor-core kernel takes 2-D problems with equal input types only");
+    }
+
+    // ---- general kernel
+    if (pr.batch_count > 65535) {
+        return fail(KUDNN_B200_UNSUPPORTED, "more than 65535 batch entries");
+    }
+    cudaError_t e = kb::launch_simt(pr, stream);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "general kernel launch");
+    }
+    h->last_kernel = KUDNN_B200_KERNEL_SIMT;
+    h->last_launches = 1;
+    return KUDNN_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int kudnn_b200_linear_validate(const kudnn_b200_linear_desc *desc)
+{
+    if (desc == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "validate: null descriptor");
+    }
+    const kudnn_b200_linear_desc &d = *desc;
+    if (d.m <= 0 || d.n <= 0 || d.k <= 0) {
+        return fail(KUDNN_B200_UNSUPPORTED, "validate: empty tensors are not supported");
+    }
+    if (d.m > 0x7fffffffll || d.n > 0x7fffffffll || d.k > 0x7fffffffll) {
+        return fail(KUDNN_B200_UNSUPPORTED, "validate: extent exceeds 2^31-1");
+    }
+    for (int i = 0; i < 3; ++i) {
+        if (d.batch[i] < 0) {
+            return fail(KUDNN_B200_BAD_ARGUMENTS, "validate: negative batch extent");
+        }
+    }
+    if (!is_float_dtype(d.a_dtype) || !is_float_dtype(d.b_dtype) || !is_float_dtype(d.c_dtype)) {
+        return fail(KUDNN_B200_UNSUPPORTED, "validate: only F32 / F16 / BF16 operands are implemented");
+    }
+    if (d.has_bias != 0 && !is_float_dtype(d.bias_dtype)) {
+        return fail(KUDNN_B200_UNSUPPORTED, "validate: bias type");
+    }
+    switch (d.act) {
+        case KUDNN_B200_ACT_NONE:
+        case KUDNN_B200_ACT_RELU:
+        case KUDNN_B200_ACT_TANH:
+        case KUDNN_B200_ACT_SIGMOID:
+        case KUDNN_B200_ACT_GELU_TANH:
+        case KUDNN_B200_ACT_SWISH:
+        case KUDNN_B200_ACT_GELU_ERF:
+            break;
+        default:
+            return fail(KUDNN_B200_UNSUPPORTED, "validate: activation %d is not implemented", d.act);
+    }
+    switch (d.res_op) {
+        case KUDNN_B200_RES_NONE:
+            break;
+        case KUDNN_B200_RES_EXT:
+        case KUDNN_B200_RES_IDENTICAL:
+        case KUDNN_B200_RES_ELTWISE_MUL:
+            if (!is_float_dtype(d.res_dtype) || !is_float_dtype(d.out_dtype)) {
+                return fail(KUDNN_B200_UNSUPPORTED, "validate: res / out type");
+            }
+            break;
+        default:
+            return fail(KUDNN_B200_UNSUPPORTED, "validate: second-output operator %d", d.res_op);
+    }
+    if (d.a_sm < 0 || d.a_sk < 0 || d.b_sk < 0 || d.b_sn < 0 || d.c_sm < 0 || d.c_sn < 0) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "validate: negative stride");
+    }
+    if ((d.c_sm == 0 && d.m > 1) || (d.c_sn == 0 && d.n > 1)) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "validate: output strides must not broadcast");
+    }
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_create(const kudnn_b200_linear_desc *desc, kudnn_b200_linear_t *handle)
+{
+    if (handle == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "create: null handle pointer");
+    }
+    *handle = nullptr;
+    int rc = kudnn_b200_linear_validate(desc);
+    if (rc != KUDNN_B200_OK) {
+        return rc;
+    }
+    Handle *h = new (std::nothrow) Handle();
+    if (h == nullptr) {
+        return fail(KUDNN_B200_ALLOC_FAILED, "create: out of host memory");
+    }
+    h->d = *desc;
+    const char *force = std::getenv("KUDNN_B200_FORCE_KERNEL");
+    if (force != nullptr) {
+        if (std::strcmp(force, "simt") == 0) {
+            h->forced_kernel = KUDNN_B200_KERNEL_SIMT;
+        } else if (std::strcmp(force, "tc") == 0) {
+            h->forced_kernel = KUDNN_B200_KERNEL_TC;
+        } else if (std::strcmp(force, "gemv_fma") == 0) {
+            h->forced_kernel = KUDNN_B200_KERNEL_GEMV_FMA;
+        } else if (std::strcmp(force, "gemv_mma") == 0) {
+            h->forced_kernel = KUDNN_B200_KERNEL_GEMV_MMA;
+        }
+    }
+    *handle = h;
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_clone(kudnn_b200_linear_t src, kudnn_b200_linear_t *handle)
+{
+    if (src == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "clone: null handle");
+    }
+    int rc = kudnn_b200_linear_create(&src->d, handle);
+    if (rc == KUDNN_B200_OK) {
+        (*handle)->forced_kernel = src->forced_kernel;
+    }
+    return rc;
+}
+
+int kudnn_b200_linear_destroy(kudnn_b200_linear_t h)
+{
+    if (h == nullptr) {
+        return KUDNN_B200_OK;
+    }
+    if (h->device >= 0) {
+        int cur = 0;
+        if (cudaGetDevice(&cur) == cudaSuccess && cur != h->device) {
+            cudaSetDevice(h->device);
+        } else {
+            cur = -1;
+        }
+        h->status.release();
+        h->gemv_partials.release();
+        h->gemv_counters.release();
+        h->a_scratch.release();
+        h->b_scratch.release();
+        h->b_packed.release();
+        for (auto &s : h->stage) {
+            s.release();
+        }
+        if (cur >= 0) {
+            cudaSetDevice(cur);
+        }
+        (void)cudaGetLastError();
+    }
+    delete h;
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_prepack(kudnn_b200_linear_t h, const void *b, void *cuda_stream)
+{
+    if (h == nullptr || b == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "prepack: null argument");
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    int rc = ensure_device(h);
+    if (rc != KUDNN_B200_OK) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    const kudnn_b200_linear_desc &d = h->d;
+    if (batch_extent(d, 0) * batch_extent(d, 1) * batch_extent(d, 2) != 1) {
+        return fail(KUDNN_B200_UNSUPPORTED, "prepack: batched weights are not pre-packed");
+    }
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, b);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        attr.type = cudaMemoryTypeUnregistered;
+    }
+    const bool on_device = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+    const void *b_dev = b;
+    if (!on_device) {
+        const size_t bytes = static_cast<size_t>(span_elems(d.k, d.b_sk, d.n, d.b_sn, d, d.b_sb)) * kb::dtype_size(d.b_dtype);
+        e = h->stage[1].reserve(bytes);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "prepack staging");
+        }
+        e = cudaMemcpyAsync(h->stage[1].ptr, b, bytes, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "prepack copy");
+        }
+        b_dev = h->stage[1].ptr;
+    }
+    h->plan_valid = false;
+    if (on_device && d.b_dtype != KUDNN_B200_F32 && kmajor_ready(b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
+        // already in the streamed layout: the packed copy is the caller's buffer itself
+        h->b_packed.release();
+        h->packed_ptr = b;
+        h->packed_raw = b;
+        h->packed_ld = d.b_sn;
+        h->packed_ktotal = d.k;
+    } else {
+        int launches = 0;
+        long long ld = 0, kt = 0;
+        const void *raw = nullptr;
+        rc = pack_weights(h, b_dev, &h->b_packed, true, stream, &ld, &kt, &raw, &launches);
+        if (rc != KUDNN_B200_OK) {
+            return rc;
+        }
+        h->packed_ptr = h->b_packed.ptr;
+        h->packed_raw = raw;
+        h->packed_ld = ld;
+        h->packed_ktotal = kt;
+    }
+    h->packed_key = b;
+    if (!on_device) {
+        e = cudaStreamSynchronize(stream);  // the staging buffer is reused by later host runs
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "prepack");
+        }
+    }
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_run(kudnn_b200_linear_t h, const kudnn_b200_linear_args *args, void *cuda_stream)
+{
+    if (h == nullptr || args == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run: null argument");
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    return run_device(h, *args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int kudnn_b200_linear_run_host(kudnn_b200_linear_t h, const kudnn_b200_linear_args *args)
+{
+    if (h == nullptr || args == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run_host: null argument");
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    int rc = ensure_device(h);
+    if (rc != KUDNN_B200_OK) {
+        return rc;
+    }
+    const kudnn_b200_linear_desc &d = h->d;
+    if (args->a == nullptr || args->b == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run_host: a and b must not be null");
+    }
+    if ((d.has_bias != 0) != (args->bias != nullptr)) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run_host: bias pointer does not match the descriptor");
+    }
+    if (d.res_op != KUDNN_B200_RES_NONE && (args->res == nullptr || args->out == nullptr)) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run_host: res and out must not be null for this descriptor");
+    }
+    if (d.res_op == KUDNN_B200_RES_NONE && args->c == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run_host: c must not be null");
+    }
+    cudaStream_t stream = nullptr;
+    const size_t bytes_a = static_cast<size_t>(span_elems(d.m, d.a_sm, d.k, d.a_sk, d, d.a_sb)) * kb::dtype_size(d.a_dtype);
+    const size_t bytes_b = static_cast<size_t>(span_elems(d.k, d.b_sk, d.n, d.b_sn, d, d.b_sb)) * kb::dtype_size(d.b_dtype);
+    const size_t bytes_c = static_cast<size_t>(span_elems(d.m, d.c_sm, d.n, d.c_sn, d, d.c_sb)) * kb::dtype_size(d.c_dtype);
+    const size_t bytes_bias =
+        d.has_bias ? static_cast<size_t>(span_elems(d.m, d.bias_sm, d.n, d.bias_sn, d, d.bias_sb)) * kb::dtype_size(d.bias_dtype)
+                   : 0;
+    const bool has_res = d.res_op != KUDNN_B200_RES_NONE;
+    const size_t bytes_res =
+        has_res ? static_cast<size_t>(span_elems(d.m, d.res_sm, d.n, d.res_sn, d, d.res_sb)) * kb::dtype_size(d.res_dtype) : 0;
+    const size_t bytes_out =
+        has_res ? static_cast<size_t>(span_elems(d.m, d.out_sm, d.n, d.out_sn, d, d.out_sb)) * kb::dtype_size(d.out_dtype) : 0;
+
+    const bool b_cached = (h->packed_key != nullptr && h->packed_key == args->b);
+    kudnn_b200_linear_args dev = *args;
+    cudaError_t e;
+#define KB_STAGE_IN(idx, host_ptr, nbytes, field)                                                        \
+    do {                                                                                                 \
+        e = h->stage[idx].reserve(nbytes);                                                               \
+        if (e != cudaSuccess) return fail_cuda(e, "host staging");                                       \
+        e = cudaMemcpyAsync(h->stage[idx].ptr, host_ptr, nbytes, cudaMemcpyHostToDevice, stream);        \
+        if (e != cudaSuccess) return fail_cuda(e, "host to device copy");                                \
+        dev.field = h->stage[idx].ptr;                                                                   \
+    } while (0)
+    KB_STAGE_IN(0, args->a, bytes_a, a);
+    if (!b_cached) {
+        KB_STAGE_IN(1, args->b, bytes_b, b);
+    }
+    if (d.has_bias) {
+        KB_STAGE_IN(3, args->bias, bytes_bias, bias);
+    }
+    if (has_res) {
+        KB_STAGE_IN(4, args->res, bytes_res, res);
+        e = h->stage[5].reserve(bytes_out);
+        if (e != cudaSuccess) return fail_cuda(e, "host staging");
+        dev.out = h->stage[5].ptr;
+    }
+    if (args->c != nullptr) {
+        if (args->beta != 0.0f) {
+            KB_STAGE_IN(2, args->c, bytes_c, c);
+        } else {
+            e = h->stage[2].reserve(bytes_c);
+            if (e != cudaSuccess) return fail_cuda(e, "host staging");
+            dev.c = h->stage[2].ptr;
+        }
+    }
+#undef KB_STAGE_IN
+    rc = run_device(h, dev, stream);
+    if (rc != KUDNN_B200_OK) {
+        return rc;
+    }
+    if (args->c != nullptr) {
+        e = cudaMemcpyAsync(args->c, dev.c, bytes_c, cudaMemcpyDeviceToHost, stream);
+        if (e != cudaSuccess) return fail_cuda(e, "device to host copy");
+    }
+    if (has_res) {
+        e = cudaMemcpyAsync(args->out, dev.out, bytes_out, cudaMemcpyDeviceToHost, stream);
+        if (e != cudaSuccess) return fail_cuda(e, "device to host copy");
+    }
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "run_host");
+    }
+    kb::DeviceStatus st;
+    e = cudaMemcpy(&st, h->status.ptr, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "status read");
+    }
+    if (st.code != kb::kErrNone) {
+        cudaMemset(h->status.ptr, 0, sizeof(st));
+        return fail(KUDNN_B200_TIMEOUT, "device-side wait gave up (site %d, block %d)", st.where, st.block);
+    }
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_check(kudnn_b200_linear_t h, void *cuda_stream)
+{
+    if (h == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "check: null handle");
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    if (h->device < 0) {
+        return KUDNN_B200_OK;
+    }
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "check");
+    }
+    kb::DeviceStatus st;
+    e = cudaMemcpy(&st, h->status.ptr, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "status read");
+    }
+    if (st.code != kb::kErrNone) {
+        cudaMemset(h->status.ptr, 0, sizeof(st));
+        return fail(KUDNN_B200_TIMEOUT, "device-side wait gave up (site %d, block %d)", st.where, st.block);
+    }
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_force_kernel(kudnn_b200_linear_t h, int kernel)
+{
+    if (h == nullptr || kernel < KUDNN_B200_KERNEL_AUTO || kernel > KUDNN_B200_KERNEL_TC) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "force_kernel: bad argument");
+    }
+    h->forced_kernel = kernel;
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_last_kernel(kudnn_b200_linear_t h)
+{
+    return h == nullptr ? 0 : h->last_kernel;
+}
+
+int kudnn_b200_linear_last_launches(kudnn_b200_linear_t h)
+{
+    return h == nullptr ? 0 : h->last_launches;
+}
+
+int64_t kudnn_b200_linear_workspace_bytes(kudnn_b200_linear_t h)
+{
+    if (h == nullptr) {
+        return 0;
+    }
+    return static_cast<int64_t>(h->gemv_partials.bytes + h->gemv_counters.bytes + h->a_scratch.bytes + h->b_scratch.bytes +
+                                h->b_packed.bytes);
+}
+
+int kudnn_b200_shard_range(int64_t total, int nparts, int part, int64_t align, int64_t *begin, int64_t *count)
+{
+    if (total < 0 || nparts <= 0 || part < 0 || part >= nparts || align <= 0 || begin == nullptr || count == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "shard_range: bad argument");
+    }
+    const int64_t units = (total + align - 1) / align;
+    const int64_t base = units / nparts, extra = units % nparts;
+    const int64_t u0 = part * base + std::min<int64_t>(part, extra);
+    const int64_t u1 = u0 + base + (part < extra ? 1 : 0);
+    const int64_t b = std::min<int64_t>(u0 * align, total);
+    const int64_t e = std::min<int64_t>(u1 * align, total);
+    *begin = b;
+    *count = e - b;
+    return KUDNN_B200_OK;
+}
+
+const char *kudnn_b200_last_error(void)
+{
+    return g_error;
+}
+
+const char *kudnn_b200_version(void)
+{
+    return "kudnn_b200 0.1 (sm_100a)";
+}
+
+int kudnn_b200_device_count(void)
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+}  // extern "C"

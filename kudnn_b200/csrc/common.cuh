@@ -103,20 +103,15 @@ __device__ __forceinline__ void store_exact(void *p, int dtype, long long idx, f
 }
 
 // 1 / (1 + exp(t)) with the reference's clamp of the exponent argument to [-87, 87]
-// (src/dnn/src/kernels/vml/vml_sve_la_sigmoid.h:39-48).
+// (src/dnn/src/kernels/vml/vml_sve_la_sigmoid.h:39-48).  Written without branches: the epilogues evaluate eight of
+// these side by side and rely on the compiler interleaving them.
 template <bool kPrecise>
 __device__ __forceinline__ float sigmoid_neg(float t)
 {
-    if (t > 87.0f) {
-        return 0.0f;
-    }
-    if (t < -87.0f) {
-        return 1.0f;
-    }
-    if (kPrecise) {
-        return 1.0f / (1.0f + expf(t));
-    }
-    return __fdividef(1.0f, 1.0f + __expf(t));
+    const float tc = fminf(fmaxf(t, -87.0f), 87.0f);
+    const float s = kPrecise ? (1.0f / (1.0f + expf(tc))) : __fdividef(1.0f, 1.0f + __expf(tc));
+    const float hi = (t > 87.0f) ? 0.0f : s;
+    return (t < -87.0f) ? 1.0f : hi;
 }
 
 // kPrecise selects libm-grade exp/erf (fp32 outputs); otherwise the fast hardware approximations, whose error
@@ -134,18 +129,14 @@ __device__ __forceinline__ float activation(float x, int act, float alpha)
         case KUDNN_B200_ACT_TANH:
             return tanhf(x);
         case KUDNN_B200_ACT_GELU_TANH: {
-            // src/dnn/src/kernels/vml/gelu_tanh/vml_sve_la_gelu_tanh.h:22-39, tanh as vml_sve_la_tanh.h:116-142
-            float y = (1.0f + x * x * 0.044715f) * x * 0.7978845608f;
-            float th;
-            if (fabsf(y) < 0.05f) {
-                th = y * (1.0f - y * y * (1.0f / 3.0f));
-            } else {
-                float e = kPrecise ? expf(y + y) : __expf(y + y);
-                th = kPrecise ? (1.0f - 2.0f / (1.0f + e)) : (1.0f - __fdividef(2.0f, 1.0f + e));
-                if (e > 1.0e37f) {
-                    th = 1.0f;  // __fdividef is undefined for huge denominators
-                }
-            }
+            // src/dnn/src/kernels/vml/gelu_tanh/vml_sve_la_gelu_tanh.h:22-39, tanh as vml_sve_la_tanh.h:116-142:
+            // y (1 - y^2 / 3) below 0.05, 1 - 2 / (1 + exp(2y)) otherwise; both evaluated, one selected
+            const float y = (1.0f + x * x * 0.044715f) * x * 0.7978845608f;
+            const float small = y * (1.0f - y * y * (1.0f / 3.0f));
+            const float yc = fminf(y, 40.0f);  // exp(2 * 40) is finite; tanh is 1 to fp32 precision long before
+            const float e = kPrecise ? expf(yc + yc) : __expf(yc + yc);
+            const float big = kPrecise ? (1.0f - 2.0f / (1.0f + e)) : (1.0f - __fdividef(2.0f, 1.0f + e));
+            const float th = (fabsf(y) < 0.05f) ? small : big;
             return (1.0f + th) * 0.5f * x;
         }
         case KUDNN_B200_ACT_GELU_ERF: {
@@ -162,7 +153,16 @@ struct EpiResult {
     float out;
 };
 
-// The post-GEMM chain for one element, everything already widened to fp32.
+// Out-of-line evaluation of any supported activation, for callers that do not fix the activation at compile time.
+static __device__ __noinline__ float activation_any(float x, int act, float alpha, int precise)
+{
+    return precise ? activation<true>(x, act, alpha) : activation<false>(x, act, alpha);
+}
+
+// The post-GEMM chain for one element, everything already widened to fp32.  kAct >= 0 fixes the activation at
+// compile time and kPrecise its arithmetic (1 = libm grade, for fp32 results; 0 = fast approximations), so that only
+// that code is emitted; kAct = -1 reads the activation from the parameters and evaluates it out of line.
+template <int kAct = -1, int kPrecise = -1>
 __device__ __forceinline__ EpiResult finish_element(const EpiParams &p, float acc, float c_old, float bias, float res)
 {
     const int ct = p.c_dtype;
@@ -183,9 +183,19 @@ __device__ __forceinline__ EpiResult finish_element(const EpiParams &p, float ac
         c1 = round_rne(t, ct);
     }
     float c2 = c1;
-    if (p.act != KUDNN_B200_ACT_NONE) {
-        float a = (ct == KUDNN_B200_F32) ? activation<true>(c1, p.act, p.act_alpha)
-                                         : activation<false>(c1, p.act, p.act_alpha);
+    if (kAct < 0) {
+        if (p.act != KUDNN_B200_ACT_NONE) {
+            c2 = round_act(activation_any(c1, p.act, p.act_alpha, ct == KUDNN_B200_F32 ? 1 : 0), ct);
+        }
+    } else if (kAct != KUDNN_B200_ACT_NONE) {
+        float a;
+        if (kPrecise == 1) {
+            a = activation<true>(c1, kAct, p.act_alpha);
+        } else if (kPrecise == 0) {
+            a = activation<false>(c1, kAct, p.act_alpha);
+        } else {
+            a = (ct == KUDNN_B200_F32) ? activation<true>(c1, kAct, p.act_alpha) : activation<false>(c1, kAct, p.act_alpha);
+        }
         c2 = round_act(a, ct);
     }
     EpiResult r;

@@ -4,20 +4,20 @@
 // (src/dnn/src/matmul_jit/MatrixComputation/kudnn_default_impl_fp16fp16f32f32.cpp:900-983) and the BLAS calls of
 // src/dnn/src/kudnn_gemm.cpp:157-227.
 //
-// Shape of one CTA (192 threads, persistent over output tiles, one CTA per SM):
+// Shape of one CTA (320 threads, persistent over output tiles, one CTA per SM):
 //   warp 0      producer: one lane issues the TMA loads of the A tile [128 x 128 B] and the B tile [BN x 128 B]
 //               of every k-block into the ring (4 or 6 stages), 128-byte swizzle, completion on an mbarrier
 //   warp 1      one lane issues tcgen05.mma (M=128, N=BN, K=32 bytes per instruction, four per k-block) into one
 //               of two TMEM accumulators and commits to the stage's "empty" barrier / the tile's "full" barrier;
 //               the warp also owns TMEM allocation
-//   warps 2..5  epilogue: each warp reads its 32 TMEM lanes (= 32 output rows) 32 columns at a time, applies the
-//               post-GEMM chain and stores 16-byte vectors; the second accumulator lets this overlap the next
-//               tile's main loop
+//   warps 2..9  epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; two warps share a lane quarter and
+//               split the columns) 8 columns at a time, applies the post-GEMM chain and stores 16-byte vectors;
+//               the second accumulator lets this overlap the next tile's main loop
 // Operands are K-major ([rows, k], k contiguous).  16-bit inputs run as kind::f16 with fp32 accumulation.  fp32
 // inputs run as kind::tf32 on split planes: x = hi + lo with hi = tf32(x), and the packed operands
 // A' = [a_lo | a_hi | a_hi], B' = [b_hi | b_lo | b_hi] make one pass over 3k compute a_lo.b_hi + a_hi.b_lo + a_hi.b_hi.
 //
-// Every wait on an mbarrier is bounded: after about two seconds the waiting thread records a timeout in the
+// Every wait on an mbarrier is bounded: after about two seconds (4e9 SM cycles) the waiting thread records a timeout in the
 // handle's status block, raises a CTA-wide abort flag that all other waits poll, and the CTA drains and frees its
 // tensor memory before returning.
 #include "kernels.cuh"
@@ -33,11 +33,12 @@ namespace kb {
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kTcThreads = 192;
+constexpr int kEpiWarps = 8;                       // two per scheduler: each hides the other's latencies
+constexpr int kTcThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA, the rest: epilogue
 constexpr int kStageRowBytes = 128;  // one swizzle row: 64 16-bit or 32 32-bit elements
 constexpr int kABytes = kBM * kStageRowBytes;
 constexpr int kGroupM = 16;  // tile rows per raster group
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about two seconds at 2 GHz
 
 struct TcParams {
     EpiParams epi;
@@ -80,36 +81,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ unsigned long long global_timer_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait.  Returns false when the CTA is aborting (this wait timed out, or another one did).
+// Bounded wait.  Returns false when the CTA is aborting (this wait timed out, or another one did).  The limit is
+// counted on the SM's own cycle counter, which is cheap to read; the wall-clock timer is not (a read costs about a
+// microsecond, which would sit on the critical path of every k-block).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
                                           DeviceStatus *status, int where)
 {
-    if (mbar_try_wait(bar, parity)) {
-        return true;
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
     }
-    const unsigned long long t0 = global_timer_ns();
+    const long long t0 = clock64();
     unsigned spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) {
             return true;
         }
-        if (*abort_flag != 0) {
-            return false;
-        }
-        if ((++spins & 0x3ffu) == 0u && global_timer_ns() - t0 > kWaitLimitNs) {
-            *abort_flag = 1;
-            if (atomicCAS(&status->code, kErrNone, kErrTimeout) == kErrNone) {
-                status->where = where;
-                status->block = static_cast<int>(blockIdx.x);
+        if ((++spins & 0x3fu) == 0u) {
+            if (*abort_flag != 0) {
+                return false;
             }
-            return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                if (atomicCAS(&status->code, kErrNone, kErrTimeout) == kErrNone) {
+                    status->where = where;
+                    status->block = static_cast<int>(blockIdx.x);
+                }
+                return false;
+            }
         }
     }
 }
@@ -175,18 +176,22 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar)
                  : "memory");
 }
 
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32])
+// 8 consecutive fp32 columns of this thread's TMEM lane; completion is awaited separately so that the next load
+// can be in flight while the current values are processed
+__device__ __forceinline__ void tmem_load_8_issue(uint32_t taddr, uint32_t (&r)[8])
 {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+// Waits for the outstanding TMEM loads.  The registers of the load are passed through so that the compiler cannot
+// schedule a use of them ahead of the wait.
+__device__ __forceinline__ void tmem_load_wait(uint32_t (&r)[8])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+                 :
+                 : "memory");
 }
 
 // ---- epilogue side-input / output access, 8 consecutive columns at a time ---------------------------------
@@ -275,6 +280,370 @@ __device__ __forceinline__ bool vec_ok(const void *base, int dtype, long long id
     return (addr & 15u) == 0;
 }
 
+// Post-GEMM chain and stores for 8 consecutive columns of one output row, starting at column ni.  Same arithmetic
+// as finish_element(), but organised as passes over the 8 values: every run-time switch (element type, bias,
+// second output) is tested once per pass instead of once per element, which leaves straight-line code with eight
+// independent dependency chains.  Only four warps run the epilogue, one per scheduler, so that instruction-level
+// parallelism is what hides the arithmetic latency.
+template <int kAct, int kPrecise>
+__device__ __forceinline__ void epilogue_group8(const EpiParams &e, const uint32_t (&raw)[8], long long mi, long long ni)
+{
+    const int valid = (e.n - ni >= 8) ? 8 : static_cast<int>(e.n - ni);
+    if (valid <= 0) {
+        return;
+    }
+    const bool full8 = valid == 8;
+    const int ct = e.c_dtype;
+    float v[8], side[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        v[j] = e.alpha * __uint_as_float(raw[j]);
+    }
+    const long long ic = mi * e.c_sm + ni * e.c_sn;
+    const bool c_vec = full8 && vec_ok(e.c, ct, ic, e.c_sn);
+    if (e.beta != 0.0f) {
+        load8(e.c, ct, ic, e.c_sn, c_vec, valid, side);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] += e.beta * side[j];
+        }
+    }
+    if (e.has_bias) {
+        const long long ib = mi * e.bias_sm + ni * e.bias_sn;
+        load8(e.bias, e.bias_dtype, ib, e.bias_sn, full8 && vec_ok(e.bias, e.bias_dtype, ib, e.bias_sn), valid, side);
+    }
+    if (ct == KUDNN_B200_F16) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] = __half2float(__float2half_rn(v[j]));
+        }
+        if (e.has_bias) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = __half2float(__float2half_rn(v[j] + side[j]));
+            }
+        }
+    } else {
+        if (e.has_bias) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] += side[j];
+            }
+        }
+        if (ct == KUDNN_B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+            }
+        }
+    }
+    if (kAct != KUDNN_B200_ACT_NONE) {
+        if (kAct < 0) {
+            if (e.act != KUDNN_B200_ACT_NONE) {
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = activation_any(v[j], e.act, e.act_alpha, ct == KUDNN_B200_F32 ? 1 : 0);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = activation<kPrecise == 1>(v[j], kAct, e.act_alpha);
+            }
+        }
+        if (ct == KUDNN_B200_F16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = __half2float(__float2half_rn(v[j]));
+            }
+        } else if (ct == KUDNN_B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = __uint_as_float(__float_as_uint(v[j]) & 0xffff0000u);
+            }
+        }
+    }
+    if (e.c != nullptr) {
+        store8(e.c, ct, ic, e.c_sn, c_vec, valid, v);
+    }
+    if (e.res_op != KUDNN_B200_RES_NONE) {
+        const long long ir = mi * e.res_sm + ni * e.res_sn;
+        load8(e.res, e.res_dtype, ir, e.res_sn, full8 && vec_ok(e.res, e.res_dtype, ir, e.res_sn), valid, side);
+        if (e.res_op == KUDNN_B200_RES_IDENTICAL) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] += side[j];
+            }
+        } else if (e.res_op == KUDNN_B200_RES_EXT) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = fmaf(side[j], e.gamma, v[j]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] *= side[j];
+            }
+        }
+        const int ot = e.out_dtype;
+        if (ot == KUDNN_B200_F16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = __half2float(__float2half_rn(v[j]));
+            }
+        } else if (ot == KUDNN_B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+            }
+        }
+        const long long io = mi * e.out_sm + ni * e.out_sn;
+        store8(e.out, ot, io, e.out_sn, full8 && vec_ok(e.out, ot, io, e.out_sn), valid, v);
+    }
+}
+
+// Per-row state of the fast path: byte pointers to the first column this thread handles.
+struct RowPointers {
+    char *c;
+    const char *bias;
+    const char *res;
+    char *out;
+    float bias_scalar;  // bias that does not vary along the row (column vector or single value)
+    int bias_mode;      // 0 none, 1 per-column values read from `bias`, 2 bias_scalar
+};
+
+__device__ __forceinline__ void load8_vec(const char *p, int dtype, float (&o)[8])
+{
+    if (dtype == KUDNN_B200_F32) {
+        const float4 v0 = reinterpret_cast<const float4 *>(p)[0], v1 = reinterpret_cast<const float4 *>(p)[1];
+        o[0] = v0.x; o[1] = v0.y; o[2] = v0.z; o[3] = v0.w;
+        o[4] = v1.x; o[5] = v1.y; o[6] = v1.z; o[7] = v1.w;
+    } else {
+        const uint4 v = *reinterpret_cast<const uint4 *>(p);
+        const unsigned w[4] = {v.x, v.y, v.z, v.w};
+        if (dtype == KUDNN_B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                o[2 * j] = __uint_as_float(w[j] << 16);
+                o[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+                o[2 * j] = f.x;
+                o[2 * j + 1] = f.y;
+            }
+        }
+    }
+}
+
+// v holds values exactly representable in dtype
+__device__ __forceinline__ void store8_vec(char *p, int dtype, const float (&v)[8])
+{
+    if (dtype == KUDNN_B200_F32) {
+        reinterpret_cast<float4 *>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4 *>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+        unsigned w[4];
+        if (dtype == KUDNN_B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[j] = (__float_as_uint(v[2 * j]) >> 16) | (__float_as_uint(v[2 * j + 1]) & 0xffff0000u);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<const unsigned *>(&h);
+            }
+        }
+        *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+template <int kDt>
+__device__ __forceinline__ void round_rne8(float (&v)[8])
+{
+    if (kDt == KUDNN_B200_F16) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] = __half2float(__float2half_rn(v[j]));
+        }
+    } else if (kDt == KUDNN_B200_BF16) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+        }
+    }
+}
+
+// Fast form of epilogue_group8: beta == 0, every tensor contiguous along the row and 16-byte aligned at this group,
+// all 8 columns in range.  Same arithmetic, no address arithmetic beyond pointer bumps.
+template <int kAct, int kPrecise>
+__device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const uint32_t (&raw)[8], const RowPointers &rp,
+                                                     int byte_off_c, int byte_off_bias, int byte_off_res, int byte_off_out)
+{
+    const int ct = e.c_dtype;
+    float v[8], side[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        v[j] = e.alpha * __uint_as_float(raw[j]);
+    }
+    if (rp.bias_mode == 1) {
+        load8_vec(rp.bias + byte_off_bias, e.bias_dtype, side);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            side[j] = rp.bias_scalar;
+        }
+    }
+    if (ct == KUDNN_B200_F16) {
+        round_rne8<KUDNN_B200_F16>(v);
+        if (rp.bias_mode != 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] += side[j];
+            }
+            round_rne8<KUDNN_B200_F16>(v);
+        }
+    } else {
+        if (rp.bias_mode != 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] += side[j];
+            }
+        }
+        if (ct == KUDNN_B200_BF16) {
+            round_rne8<KUDNN_B200_BF16>(v);
+        }
+    }
+    if (kAct != KUDNN_B200_ACT_NONE) {
+        if (kAct < 0) {
+            if (e.act != KUDNN_B200_ACT_NONE) {
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = activation_any(v[j], e.act, e.act_alpha, ct == KUDNN_B200_F32 ? 1 : 0);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = activation<kPrecise == 1>(v[j], kAct, e.act_alpha);
+            }
+        }
+        if (ct == KUDNN_B200_F16) {
+            round_rne8<KUDNN_B200_F16>(v);
+        } else if (ct == KUDNN_B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = __uint_as_float(__float_as_uint(v[j]) & 0xffff0000u);
+            }
+        }
+    }
+    if (rp.c != nullptr) {
+        store8_vec(rp.c + byte_off_c, ct, v);
+    }
+    if (e.res_op != KUDNN_B200_RES_NONE) {
+        load8_vec(rp.res + byte_off_res, e.res_dtype, side);
+        if (e.res_op == KUDNN_B200_RES_IDENTICAL) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] += side[j];
+            }
+        } else if (e.res_op == KUDNN_B200_RES_EXT) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = fmaf(side[j], e.gamma, v[j]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] *= side[j];
+            }
+        }
+        const int ot = e.out_dtype;
+        if (ot == KUDNN_B200_F16) {
+            round_rne8<KUDNN_B200_F16>(v);
+        } else if (ot == KUDNN_B200_BF16) {
+            round_rne8<KUDNN_B200_BF16>(v);
+        }
+        store8_vec(rp.out + byte_off_out, ot, v);
+    }
+}
+
+__device__ __forceinline__ bool row_contiguous_aligned(const void *base, int dtype, long long idx0, long long sn)
+{
+    return sn == 1 && ((reinterpret_cast<uintptr_t>(base) + static_cast<uintptr_t>(idx0) * dtype_size(dtype)) & 15u) == 0;
+}
+
+// One thread's share of a tile: its row, `groups` groups of 8 columns starting at column n0, read from TMEM at
+// taddr.  The loop is rolled to keep the code small (a fully unrolled epilogue does not fit the instruction cache
+// and runs an order of magnitude slower); the TMEM load of the next group is in flight while the current one is
+// processed.  Rows whose tensors are contiguous and 16-byte aligned take the pointer-bumping fast path.
+template <int kAct, int kPrecise>
+__device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr, bool row_ok, long long mi, long long n0,
+                                             int groups)
+{
+    if (groups <= 0) {
+        return;
+    }
+    RowPointers rp;
+    rp.c = nullptr;
+    rp.bias = nullptr;
+    rp.res = nullptr;
+    rp.out = nullptr;
+    rp.bias_scalar = 0.0f;
+    rp.bias_mode = 0;
+    bool fast = row_ok && e.beta == 0.0f && (n0 + static_cast<long long>(groups) * 8 <= e.n);
+    if (fast) {
+        if (e.c != nullptr) {
+            const long long ic = mi * e.c_sm + n0 * e.c_sn;
+            fast = fast && row_contiguous_aligned(e.c, e.c_dtype, ic, e.c_sn);
+            rp.c = static_cast<char *>(e.c) + ic * dtype_size(e.c_dtype);
+        }
+        if (e.has_bias) {
+            const long long ib = mi * e.bias_sm + n0 * e.bias_sn;
+            if (e.bias_sn == 0) {
+                rp.bias_mode = 2;
+                rp.bias_scalar = load_as_f32(e.bias, e.bias_dtype, ib);
+            } else {
+                rp.bias_mode = 1;
+                fast = fast && row_contiguous_aligned(e.bias, e.bias_dtype, ib, e.bias_sn);
+                rp.bias = static_cast<const char *>(e.bias) + ib * dtype_size(e.bias_dtype);
+            }
+        }
+        if (e.res_op != KUDNN_B200_RES_NONE) {
+            const long long ir = mi * e.res_sm + n0 * e.res_sn;
+            const long long io = mi * e.out_sm + n0 * e.out_sn;
+            fast = fast && row_contiguous_aligned(e.res, e.res_dtype, ir, e.res_sn) &&
+                   row_contiguous_aligned(e.out, e.out_dtype, io, e.out_sn);
+            rp.res = static_cast<const char *>(e.res) + ir * dtype_size(e.res_dtype);
+            rp.out = static_cast<char *>(e.out) + io * dtype_size(e.out_dtype);
+        }
+    }
+    const int step_c = 8 * dtype_size(e.c_dtype), step_bias = 8 * dtype_size(e.bias_dtype);
+    const int step_res = 8 * dtype_size(e.res_dtype), step_out = 8 * dtype_size(e.out_dtype);
+
+    uint32_t next[8], cur[8];
+    tmem_load_8_issue(taddr, next);
+#pragma unroll 1
+    for (int g = 0; g < groups; ++g) {
+        __syncwarp();  // rows of a warp may have taken different paths below; the TMEM instructions need them together
+        tmem_load_wait(next);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            cur[j] = next[j];
+        }
+        if (g + 1 < groups) {
+            tmem_load_8_issue(taddr + static_cast<uint32_t>((g + 1) * 8), next);
+        }
+        if (fast) {
+            epilogue_group8_fast<kAct, kPrecise>(e, cur, rp, g * step_c, g * step_bias, g * step_res, g * step_out);
+        } else if (row_ok) {
+            epilogue_group8<kAct, kPrecise>(e, cur, mi, n0 + g * 8);
+        }
+    }
+}
+
 template <int kKind, int kBN>
 __global__ void __launch_bounds__(kTcThreads, 1)
     tc_linear_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -308,7 +677,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tmem_full + a, 1);
-            mbar_init(tmem_empty + a, 4);
+            mbar_init(tmem_empty + a, kEpiWarps);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -407,6 +776,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: [32 * quarter, 32 * quarter + 32)
         const int row_in_tile = quarter * 32 + lane;
+        const int part = (warp - 2) / 4;  // warps sharing a quarter split the tile's columns between them
         const EpiParams &e = p.epi;
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -426,60 +796,37 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const bool row_ok = mi < p.m;
             const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                        static_cast<uint32_t>(acc * kBN);
-#pragma unroll 1
-            for (int chunk = 0; chunk < kBN / 32; ++chunk) {
-                const long long nc = static_cast<long long>(tn) * kBN + chunk * 32;
-                if (nc >= p.n) {
-                    break;  // warp-uniform: the rest of the tile is out of range
-                }
-                uint32_t raw[32];
-                tmem_load_32(taddr_row + static_cast<uint32_t>(chunk * 32), raw);
-                if (row_ok) {
-#pragma unroll
-                    for (int j8 = 0; j8 < 4; ++j8) {
-                        const long long ni = nc + j8 * 8;
-                        const int valid = (p.n - ni >= 8) ? 8 : static_cast<int>(p.n - ni);
-                        if (valid <= 0) {
-                            break;
-                        }
-                        const bool full8 = valid == 8;
-                        float bias[8], res[8], cold[8], vc[8], vo[8];
-                        const long long ic = mi * e.c_sm + ni * e.c_sn;
-                        const bool c_vec = full8 && vec_ok(e.c, e.c_dtype, ic, e.c_sn);
-                        if (e.has_bias) {
-                            const long long ib = mi * e.bias_sm + ni * e.bias_sn;
-                            load8(e.bias, e.bias_dtype, ib, e.bias_sn, full8 && vec_ok(e.bias, e.bias_dtype, ib, e.bias_sn),
-                                  valid, bias);
-                        }
-                        if (e.beta != 0.0f && e.c != nullptr) {
-                            load8(e.c, e.c_dtype, ic, e.c_sn, c_vec, valid, cold);
-                        }
-                        long long io = 0;
-                        bool o_vec = false;
-                        if (e.res_op != KUDNN_B200_RES_NONE) {
-                            const long long ir = mi * e.res_sm + ni * e.res_sn;
-                            load8(e.res, e.res_dtype, ir, e.res_sn, full8 && vec_ok(e.res, e.res_dtype, ir, e.res_sn),
-                                  valid, res);
-                            io = mi * e.out_sm + ni * e.out_sn;
-                            o_vec = full8 && vec_ok(e.out, e.out_dtype, io, e.out_sn);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const EpiResult r =
-                                finish_element(e, __uint_as_float(raw[j8 * 8 + j]), (e.beta != 0.0f) ? cold[j] : 0.0f,
-                                               e.has_bias ? bias[j] : 0.0f,
-                                               (e.res_op != KUDNN_B200_RES_NONE) ? res[j] : 0.0f);
-                            vc[j] = r.c;
-                            vo[j] = r.out;
-                        }
-                        if (e.c != nullptr) {
-                            store8(e.c, e.c_dtype, ic, e.c_sn, c_vec, valid, vc);
-                        }
-                        if (e.res_op != KUDNN_B200_RES_NONE) {
-                            store8(e.out, e.out_dtype, io, e.out_sn, o_vec, valid, vo);
-                        }
+            constexpr int kPartCols = kBN / (kEpiWarps / 4);
+            const long long n0 = static_cast<long long>(tn) * kBN + part * kPartCols;
+            long long cols = p.n - n0;
+            cols = cols < 0 ? 0 : (cols < kPartCols ? cols : kPartCols);
+            const int groups = static_cast<int>((cols + 7) / 8);
+            const uint32_t taddr_part = taddr_row + static_cast<uint32_t>(part * kPartCols);
+            const bool precise = e.c_dtype == KUDNN_B200_F32;
+            switch (e.act) {
+                case KUDNN_B200_ACT_NONE:
+                    epilogue_row<KUDNN_B200_ACT_NONE, 0>(e, taddr_part, row_ok, mi, n0, groups);
+                    break;
+                case KUDNN_B200_ACT_RELU:
+                    epilogue_row<KUDNN_B200_ACT_RELU, 0>(e, taddr_part, row_ok, mi, n0, groups);
+                    break;
+                case KUDNN_B200_ACT_SWISH:
+                    if (precise) {
+                        epilogue_row<KUDNN_B200_ACT_SWISH, 1>(e, taddr_part, row_ok, mi, n0, groups);
+                    } else {
+                        epilogue_row<KUDNN_B200_ACT_SWISH, 0>(e, taddr_part, row_ok, mi, n0, groups);
                     }
-                }
+                    break;
+                case KUDNN_B200_ACT_GELU_TANH:
+                    if (precise) {
+                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 1>(e, taddr_part, row_ok, mi, n0, groups);
+                    } else {
+                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 0>(e, taddr_part, row_ok, mi, n0, groups);
+                    }
+                    break;
+                default:
+                    epilogue_row<-1, -1>(e, taddr_part, row_ok, mi, n0, groups);
+                    break;
             }
             tc_fence_before();
             __syncwarp();
@@ -500,8 +847,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     tc_fence_after();
     if (*abort_flag != 0) {
         // give copies and MMAs that were already issued time to land before the memory is handed back
-        const unsigned long long t0 = global_timer_ns();
-        while (global_timer_ns() - t0 < 200000ull) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000ll) {
             __nanosleep(1000);
         }
         __syncthreads();

@@ -193,6 +193,18 @@ def run_gpu(desc, arrays, c, device, kernel=kb.KERNEL_AUTO, prepack=False, host=
 
 FP32_NORMWISE_TOL = 1e-5      # max |y - ref| / max |ref|
 HALF_ABS_REL_TOL = 1e-2       # |y - ref| <= 1e-2 * (|ref| + 1), element-wise, for fp16 / bf16 results
+# bf16 keeps 8 significant bits: two units in the last place are up to 1.56 % of the value.  The reference chain
+# rounds twice after the GEMM (RNE after the bias, truncation after the activation), so a last-bit difference in
+# the fp32 accumulator (summation order) can move a result by one unit at each rounding.  Such elements cannot
+# always meet 1e-2 * (|ref| + 1); they are allowed if they are rare and within two units.
+HALF_OUTLIER_FRACTION = 1e-4
+HALF_OUTLIER_MAX_ULP = 2
+
+
+def _ordered(bits16):
+    """Maps 16-bit float patterns to integers whose difference is the distance in units in the last place."""
+    b = bits16.astype(np.int32)
+    return np.where(b & 0x8000, -(b & 0x7fff), b & 0x7fff)
 
 
 def compare(got, ref, code):
@@ -208,13 +220,17 @@ def compare(got, ref, code):
         assert info["normwise"] <= FP32_NORMWISE_TOL, "fp32 normwise error %.3e" % info["normwise"]
     else:
         bound = HALF_ABS_REL_TOL * (np.abs(r) + 1.0)
-        worst = float(np.max(err / bound))
-        info["worst_over_bound"] = worst
-        same = got.view(np.uint16) == ref.view(np.uint16)
-        # +0 and -0 are the same number
-        same |= (g == r)
-        info["bit_exact_fraction"] = float(np.mean(same))
-        assert worst <= 1.0, "16-bit error exceeds 1e-2*(|ref|+1) by a factor %.3f" % worst
+        over = err > bound
+        ulp = np.abs(_ordered(got.view(np.uint16)) - _ordered(ref.view(np.uint16)))
+        info["worst_over_bound"] = float(np.max(err / bound))
+        info["over_bound_fraction"] = float(np.mean(over))
+        info["max_ulp"] = int(ulp.max())
+        info["bit_exact_fraction"] = float(np.mean(ulp == 0))
+        assert info["over_bound_fraction"] <= HALF_OUTLIER_FRACTION, \
+            "%.2e of the elements exceed 1e-2*(|ref|+1)" % info["over_bound_fraction"]
+        if over.any():
+            assert int(ulp[over].max()) <= HALF_OUTLIER_MAX_ULP, \
+                "an element beyond 1e-2*(|ref|+1) is %d units away from the oracle" % int(ulp[over].max())
     return info
 
 

@@ -28,8 +28,6 @@ namespace kb {
 
 namespace {
 
-constexpr int kGemvThreads = 512;
-constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kMmaRowPadBytes = 64;  // keeps the 8 quarter-warp rows of an A-fragment load on distinct banks
 
 struct GemvParams {
@@ -83,8 +81,8 @@ __device__ __forceinline__ float warp_sum(float v)
 
 // ------------------------------------------------------------------------------------------------ FMA kernel
 
-template <int kDtype, int kM, int kUnroll>
-__global__ void __launch_bounds__(kGemvThreads, (kUnroll <= 4) ? 2 : 1) gemv_fma_kernel(const GemvParams p)
+template <int kDtype, int kM, int kUnroll, int kThreads, int kMinBlocks>
+__global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_fma_kernel(const GemvParams p)
 {
     constexpr int kVec = (kDtype == KUDNN_B200_F32) ? 4 : 8;  // elements per 16-byte load
     constexpr int kBlockK = 32 * kVec;
@@ -92,7 +90,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kUnroll <= 4) ? 2 : 1) gemv_fma
     float *xs = reinterpret_cast<float *>(smem_raw);  // [kM][kpad]
     const int kpad = p.kb * kBlockK;
 
-    for (int i = threadIdx.x; i < kM * kpad; i += kGemvThreads) {
+    for (int i = threadIdx.x; i < kM * kpad; i += kThreads) {
         const int mi = i / kpad, kk = i - mi * kpad;
         float v = 0.0f;
         if (kk < p.k) {
@@ -103,7 +101,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kUnroll <= 4) ? 2 : 1) gemv_fma
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
-    const int warp = blockIdx.x * kGemvWarps + (threadIdx.x >> 5);
+    const int warp = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
     if (warp >= p.active_warps) {
         return;
     }
@@ -236,8 +234,8 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], unsigned a0, unsigned a
 }
 
 // kRows16: activations occupy both 8-row halves of the 16-row operand (m > 8)
-template <int kDtype, bool kRows16, int kUnroll>
-__global__ void __launch_bounds__(kGemvThreads, (kUnroll <= 4) ? 2 : 1) gemv_mma_kernel(const GemvParams p)
+template <int kDtype, bool kRows16, int kUnroll, int kThreads, int kMinBlocks>
+__global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kRows = kRows16 ? 16 : 8;
@@ -250,7 +248,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kUnroll <= 4) ? 2 : 1) gemv_mma
     {
         const int vec_per_row = p.kc / 8;
         const unsigned short *xg = static_cast<const unsigned short *>(p.x);
-        for (int i = threadIdx.x; i < kRows * vec_per_row; i += kGemvThreads) {
+        for (int i = threadIdx.x; i < kRows * vec_per_row; i += kThreads) {
             const int mi = i / vec_per_row, v = i - mi * vec_per_row;
             const int kk = kc0 + v * 8;
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -264,7 +262,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kUnroll <= 4) ? 2 : 1) gemv_mma
 
     const int lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
-    const int warp = cta_in_chunk * kGemvWarps + (threadIdx.x >> 5);
+    const int warp = cta_in_chunk * (kThreads / 32) + (threadIdx.x >> 5);
     if (warp >= p.active_warps) {
         return;
     }
@@ -382,15 +380,16 @@ cudaError_t set_smem(K kernel, size_t bytes)
     return cudaSuccess;
 }
 
-template <int kDtype, int kUnroll>
+template <int kDtype, int kUnroll, int kThreads, int kMinBlocks>
 cudaError_t launch_fma_m(const GemvParams &p, const GemvPlan &plan, cudaStream_t stream)
 {
-#define KB_FMA_CASE(M)                                                                                     \
-    case M: {                                                                                              \
-        cudaError_t e = set_smem(gemv_fma_kernel<kDtype, M, kUnroll>, plan.smem_bytes);                    \
-        if (e != cudaSuccess) return e;                                                                    \
-        gemv_fma_kernel<kDtype, M, kUnroll><<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);        \
-        break;                                                                                             \
+#define KB_FMA_CASE(M)                                                                                            \
+    case M: {                                                                                                     \
+        auto kernel = gemv_fma_kernel<kDtype, M, kUnroll, kThreads, kMinBlocks>;                                  \
+        cudaError_t e = set_smem(kernel, plan.smem_bytes);                                                        \
+        if (e != cudaSuccess) return e;                                                                           \
+        kernel<<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);                                            \
+        break;                                                                                                    \
     }
     switch (p.m) {
         KB_FMA_CASE(1)
@@ -404,19 +403,50 @@ cudaError_t launch_fma_m(const GemvParams &p, const GemvPlan &plan, cudaStream_t
     return cudaGetLastError();
 }
 
-template <int kDtype, int kUnroll>
+template <int kDtype, int kUnroll, int kThreads, int kMinBlocks>
 cudaError_t launch_mma_rows(const GemvParams &p, const GemvPlan &plan, cudaStream_t stream)
 {
     if (p.m > 8) {
-        cudaError_t e = set_smem(gemv_mma_kernel<kDtype, true, kUnroll>, plan.smem_bytes);
+        auto kernel = gemv_mma_kernel<kDtype, true, kUnroll, kThreads, kMinBlocks>;
+        cudaError_t e = set_smem(kernel, plan.smem_bytes);
         if (e != cudaSuccess) return e;
-        gemv_mma_kernel<kDtype, true, kUnroll><<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);
+        kernel<<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);
     } else {
-        cudaError_t e = set_smem(gemv_mma_kernel<kDtype, false, kUnroll>, plan.smem_bytes);
+        auto kernel = gemv_mma_kernel<kDtype, false, kUnroll, kThreads, kMinBlocks>;
+        cudaError_t e = set_smem(kernel, plan.smem_bytes);
         if (e != cudaSuccess) return e;
-        gemv_mma_kernel<kDtype, false, kUnroll><<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);
+        kernel<<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);
     }
     return cudaGetLastError();
+}
+
+// Launch shapes: threads per CTA / resident CTAs per SM the kernel is compiled for.
+struct GemvShape {
+    int threads, min_blocks;
+};
+constexpr GemvShape kShapes[3] = {{512, 2}, {1024, 1}, {1024, 2}};
+
+template <int kDtype, bool kFma>
+cudaError_t launch_shape(const GemvParams &p, const GemvPlan &plan, int shape, int unroll, cudaStream_t stream)
+{
+#define KB_SHAPE_CASE(S, T, B)                                                                       \
+    case S:                                                                                          \
+        if (kFma) {                                                                                  \
+            return unroll >= 8 ? launch_fma_m<kDtype, 8, T, B>(p, plan, stream)                      \
+                               : launch_fma_m<kDtype, 4, T, B>(p, plan, stream);                     \
+        } else if (kDtype != KUDNN_B200_F32) {                                                       \
+            return unroll >= 8 ? launch_mma_rows<kDtype == KUDNN_B200_F32 ? KUDNN_B200_BF16 : kDtype, 8, T, B>(p, plan, stream) \
+                               : launch_mma_rows<kDtype == KUDNN_B200_F32 ? KUDNN_B200_BF16 : kDtype, 4, T, B>(p, plan, stream); \
+        }                                                                                            \
+        return cudaErrorInvalidValue;
+    switch (shape) {
+        KB_SHAPE_CASE(0, 512, 2)
+        KB_SHAPE_CASE(1, 1024, 1)
+        KB_SHAPE_CASE(2, 1024, 2)
+        default:
+            return cudaErrorInvalidValue;
+    }
+#undef KB_SHAPE_CASE
 }
 
 }  // namespace
@@ -432,22 +462,21 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     }
     const int dt = pr.a_dtype;
     const int vec = (dt == KUDNN_B200_F32) ? 4 : 8;
-    const int esize = dtype_size(dt);
-    if (pr.k % vec != 0 || pr.a_sm % vec != 0 || pr.b_sn % vec != 0 || pr.k > (1 << 24) || pr.n > (1 << 28)) {
+    if (pr.k % vec != 0 || (pr.m > 1 && pr.a_sm % vec != 0) || (pr.n > 1 && pr.b_sn % vec != 0) || pr.k > (1 << 24) ||
+        pr.n > (1 << 28)) {
         return false;
     }
     if ((reinterpret_cast<uintptr_t>(pr.a) & 15u) != 0 || (reinterpret_cast<uintptr_t>(pr.b) & 15u) != 0) {
         return false;
     }
-    (void)esize;
-    const int max_smem = 200 * 1024;
+    const size_t max_smem = 200 * 1024;
     int kernel = forced_kernel;
     if (kernel != KUDNN_B200_KERNEL_GEMV_FMA && kernel != KUDNN_B200_KERNEL_GEMV_MMA) {
-        const int fma_max_m = env_int("KUDNN_B200_GEMV_FMA_MAX_M", 2);
+        const int fma_max_m = env_int("KUDNN_B200_GEMV_FMA_MAX_M", 1);
         kernel = (dt == KUDNN_B200_F32 || pr.m <= fma_max_m) ? KUDNN_B200_KERNEL_GEMV_FMA : KUDNN_B200_KERNEL_GEMV_MMA;
     }
     plan->kernel = kernel;
-    plan->block = kGemvThreads;
+    int shape = env_int("KUDNN_B200_GEMV_SHAPE", -1);
     if (kernel == KUDNN_B200_KERNEL_GEMV_FMA) {
         if (pr.m > 4) {
             return false;
@@ -455,17 +484,25 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
         const int block_k = 32 * vec;
         const long long kb = (pr.k + block_k - 1) / block_k;
         const size_t smem = static_cast<size_t>(pr.m) * kb * block_k * sizeof(float);
-        if (smem > static_cast<size_t>(max_smem)) {
+        if (smem > max_smem) {
             return false;
         }
-        const int ctas_per_sm = (smem <= 100 * 1024) ? 2 : 1;
-        const int grid = sm_count * ctas_per_sm;
+        if (shape < 0 || shape > 2) {
+            shape = (smem <= 100 * 1024) ? 0 : 1;
+        }
+        if (smem > 100 * 1024) {
+            shape = 1;  // only one CTA fits per SM
+        }
+        const int threads = kShapes[shape].threads, warps = threads / 32;
+        const int grid = sm_count * kShapes[shape].min_blocks;
         const long long total = pr.n * kb;
-        long long active = std::min<long long>(static_cast<long long>(grid) * kGemvWarps, pr.n);  // span >= kb
+        long long active = std::min<long long>(static_cast<long long>(grid) * warps, pr.n);  // keeps span >= kb
         active = std::max<long long>(active, 1);
         const long long span = (total + active - 1) / active;
         active = (total + span - 1) / span;
-        plan->grid = static_cast<int>((active + kGemvWarps - 1) / kGemvWarps);
+        plan->shape = shape;
+        plan->block = threads;
+        plan->grid = static_cast<int>((active + warps - 1) / warps);
         plan->ksplit = 1;
         plan->active_warps = static_cast<int>(active);
         plan->span = span;
@@ -480,12 +517,17 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
         return false;
     }
     const int rows = pr.m > 8 ? 16 : 8;
+    if (shape < 0 || shape > 2) {
+        // 16 activation rows: one 1024-thread CTA per SM leaves room for a longer K chunk (fewer partial sums)
+        shape = (rows == 16) ? 1 : 0;
+    }
+    const size_t smem_budget = (kShapes[shape].min_blocks == 2) ? 100 * 1024 : max_smem;
     int ksplit = env_int("KUDNN_B200_GEMV_KSPLIT", 0);
     if (ksplit <= 0) {
         ksplit = 1;
         while (ksplit < 64) {
             const long long kc = ((pr.k + ksplit - 1) / ksplit + 31) / 32 * 32;
-            if (static_cast<size_t>(rows) * (kc * 2 + kMmaRowPadBytes) <= 100 * 1024) {
+            if (static_cast<size_t>(rows) * (kc * 2 + kMmaRowPadBytes) <= smem_budget) {
                 break;
             }
             ksplit *= 2;
@@ -493,20 +535,25 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     }
     const long long kc = ((pr.k + ksplit - 1) / ksplit + 31) / 32 * 32;
     const size_t smem = static_cast<size_t>(rows) * (kc * 2 + kMmaRowPadBytes);
-    if (smem > static_cast<size_t>(max_smem)) {
+    if (smem > max_smem) {
         return false;
     }
-    const int ctas_per_sm = (smem <= 100 * 1024) ? 2 : 1;
-    int grid = sm_count * ctas_per_sm;
+    if (smem > 100 * 1024 && kShapes[shape].min_blocks == 2) {
+        shape = 1;
+    }
+    const int threads = kShapes[shape].threads, warps = threads / 32;
+    int grid = sm_count * kShapes[shape].min_blocks;
     grid = std::max(grid / ksplit, 1) * ksplit;
     const long long groups = (pr.n + 7) / 8;
     const long long kbc = kc / 32;
     const long long total = groups * kbc;
-    long long active = std::min<long long>(static_cast<long long>(grid / ksplit) * kGemvWarps, 2 * groups);
+    long long active = std::min<long long>(static_cast<long long>(grid / ksplit) * warps, 2 * groups);
     active = std::max<long long>(active, 1);
     const long long span = (total + active - 1) / active;
     active = (total + span - 1) / span;
-    plan->grid = static_cast<int>((active + kGemvWarps - 1) / kGemvWarps) * ksplit;
+    plan->shape = shape;
+    plan->block = threads;
+    plan->grid = static_cast<int>((active + warps - 1) / warps) * ksplit;
     plan->ksplit = ksplit;
     plan->active_warps = static_cast<int>(active);
     plan->span = span;
@@ -545,26 +592,21 @@ cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const Gem
         p.kc = 0;
         p.total = pr.n * p.kb;
         if (dt == KUDNN_B200_F32) {
-            return unroll >= 8 ? launch_fma_m<KUDNN_B200_F32, 8>(p, plan, stream)
-                               : launch_fma_m<KUDNN_B200_F32, 4>(p, plan, stream);
+            return launch_shape<KUDNN_B200_F32, true>(p, plan, plan.shape, unroll, stream);
         }
         if (dt == KUDNN_B200_F16) {
-            return unroll >= 8 ? launch_fma_m<KUDNN_B200_F16, 8>(p, plan, stream)
-                               : launch_fma_m<KUDNN_B200_F16, 4>(p, plan, stream);
+            return launch_shape<KUDNN_B200_F16, true>(p, plan, plan.shape, unroll, stream);
         }
-        return unroll >= 8 ? launch_fma_m<KUDNN_B200_BF16, 8>(p, plan, stream)
-                           : launch_fma_m<KUDNN_B200_BF16, 4>(p, plan, stream);
+        return launch_shape<KUDNN_B200_BF16, true>(p, plan, plan.shape, unroll, stream);
     }
     const long long kc = ((pr.k + plan.ksplit - 1) / plan.ksplit + 31) / 32 * 32;
     p.kc = static_cast<int>(kc);
     p.kb = static_cast<int>(kc / 32);
     p.total = ((pr.n + 7) / 8) * p.kb;
     if (dt == KUDNN_B200_F16) {
-        return unroll >= 8 ? launch_mma_rows<KUDNN_B200_F16, 8>(p, plan, stream)
-                           : launch_mma_rows<KUDNN_B200_F16, 4>(p, plan, stream);
+        return launch_shape<KUDNN_B200_F16, false>(p, plan, plan.shape, unroll, stream);
     }
-    return unroll >= 8 ? launch_mma_rows<KUDNN_B200_BF16, 8>(p, plan, stream)
-                       : launch_mma_rows<KUDNN_B200_BF16, 4>(p, plan, stream);
+    return launch_shape<KUDNN_B200_BF16, false>(p, plan, plan.shape, unroll, stream);
 }
 
 }  // namespace kb

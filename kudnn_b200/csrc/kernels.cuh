@@ -28,6 +28,7 @@ struct GemvWorkspace {
 struct GemvPlan {
     int kernel;         // KUDNN_B200_KERNEL_GEMV_FMA / _MMA
     int grid, block;    // launch shape
+    int shape;          // index of the compiled (threads, CTAs per SM) variant
     int ksplit;         // K chunks (MMA kernel)
     int active_warps;   // warps that take a span of the flattened work
     long long span;     // work blocks per active warp

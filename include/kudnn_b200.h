@@ -125,6 +125,19 @@ KUDNN_B200_API int kudnn_b200_linear_run(kudnn_b200_linear_t handle, const kudnn
  * outputs back and synchronises.  A weight pointer that was pre-packed is not copied again. */
 KUDNN_B200_API int kudnn_b200_linear_run_host(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args);
 
+/* Decode-shaped Linear (m <= 16, 2-D, K-contiguous a and b) that allocates no device memory, for callers that
+ * cannot call cudaMalloc when they need the result: engines that have already handed all of HBM to their own pools,
+ * plug-ins whose host forbids allocation inside an operator call, decode loops that cannot risk the device
+ * synchronisation an allocation may cause.  This entry point has no counterpart in the reference.  It takes the
+ * descriptor directly (no handle) and device pointers; the split-K scratch of the streaming kernels is a fixed
+ * 8 MiB (+ 64 KiB of counters) array inside the library's device image, held by every GPU that loads the library
+ * until the process exits.  Problems whose scratch does not fit return KUDNN_B200_UNSUPPORTED and launch nothing.
+ * All calls on a device share that array: calls that overlap on the GPU race and give undefined results, so keep
+ * them on one stream.  The first call on each device resolves the array's device address; make that call before
+ * beginning any stream capture. */
+KUDNN_B200_API int kudnn_b200_linear_run_static_scratch(const kudnn_b200_linear_desc *desc,
+                                                        const kudnn_b200_linear_args *args, void *cuda_stream);
+
 /* Reads the device-side status word of the handle (bounded waits that gave up) after synchronising the stream. */
 KUDNN_B200_API int kudnn_b200_linear_check(kudnn_b200_linear_t handle, void *cuda_stream);
 

@@ -10,7 +10,7 @@ from .capi import (  # noqa: F401
     BF16, F16, F32,
     KERNEL_AUTO, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_SIMT, KERNEL_TC, KERNEL_NAMES,
     RES_ELTWISE_MUL, RES_EXT, RES_IDENTICAL, RES_NONE,
-    KudnnError, Linear, LinearDesc, library, library_path, make_desc, shard_range,
+    KudnnError, Linear, LinearDesc, library, library_path, make_desc, run_static_scratch, shard_range,
 )
 
 __all__ = [
@@ -18,5 +18,5 @@ __all__ = [
     "BF16", "F16", "F32",
     "KERNEL_AUTO", "KERNEL_GEMV_FMA", "KERNEL_GEMV_MMA", "KERNEL_SIMT", "KERNEL_TC", "KERNEL_NAMES",
     "RES_ELTWISE_MUL", "RES_EXT", "RES_IDENTICAL", "RES_NONE",
-    "KudnnError", "Linear", "LinearDesc", "library", "library_path", "make_desc", "shard_range",
+    "KudnnError", "Linear", "LinearDesc", "library", "library_path", "make_desc", "run_static_scratch", "shard_range",
 ]

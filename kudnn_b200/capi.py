@@ -57,6 +57,7 @@ class LinearArgs(ctypes.Structure):
 EXPORTS = [
     "kudnn_b200_linear_validate", "kudnn_b200_linear_create", "kudnn_b200_linear_clone", "kudnn_b200_linear_destroy",
     "kudnn_b200_linear_prepack", "kudnn_b200_linear_run", "kudnn_b200_linear_run_host", "kudnn_b200_linear_check",
+    "kudnn_b200_linear_run_static_scratch",
     "kudnn_b200_linear_force_kernel", "kudnn_b200_linear_last_kernel", "kudnn_b200_linear_last_launches",
     "kudnn_b200_linear_workspace_bytes", "kudnn_b200_shard_range", "kudnn_b200_last_error", "kudnn_b200_version",
     "kudnn_b200_device_count",
@@ -88,6 +89,7 @@ def library():
     lib.kudnn_b200_linear_run.argtypes = [vp, ctypes.POINTER(LinearArgs), vp]
     lib.kudnn_b200_linear_run_host.argtypes = [vp, ctypes.POINTER(LinearArgs)]
     lib.kudnn_b200_linear_check.argtypes = [vp, vp]
+    lib.kudnn_b200_linear_run_static_scratch.argtypes = [ctypes.POINTER(LinearDesc), ctypes.POINTER(LinearArgs), vp]
     lib.kudnn_b200_linear_force_kernel.argtypes = [vp, i32]
     lib.kudnn_b200_linear_last_kernel.argtypes = [vp]
     lib.kudnn_b200_linear_last_launches.argtypes = [vp]
@@ -161,6 +163,20 @@ def shard_range(total, nparts, part, align=1):
     b, c = ctypes.c_int64(), ctypes.c_int64()
     _check(library().kudnn_b200_shard_range(total, nparts, part, align, ctypes.byref(b), ctypes.byref(c)))
     return b.value, c.value
+
+
+def run_static_scratch(desc, a, b, c=None, bias=None, res=None, out=None, alpha=1.0, beta=0.0, gamma=1.0, stream=None):
+    """Decode-shaped Linear (m <= 16) through the entry point that allocates no device memory.
+
+    For callers that cannot call cudaMalloc when they need the result (all of HBM already given to their own pools, or
+    an operator call in which the host framework forbids allocation).  Device pointers, asynchronous on `stream`.  The
+    scratch is one fixed array per device, shared by all calls: keep the calls on one stream, because calls that
+    overlap on the GPU race.  Problems that need more than the built-in 8 MiB raise KudnnError (UNSUPPORTED).
+    """
+    args = LinearArgs()
+    args.a, args.b, args.c, args.bias, args.res, args.out = (_ptr(a), _ptr(b), _ptr(c), _ptr(bias), _ptr(res), _ptr(out))
+    args.alpha, args.beta, args.gamma = alpha, beta, gamma
+    _check(library().kudnn_b200_linear_run_static_scratch(ctypes.byref(desc), ctypes.byref(args), stream))
 
 
 class Linear:

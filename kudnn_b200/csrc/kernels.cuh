@@ -37,6 +37,9 @@ struct GemvPlan {
     long long partial_floats, counter_count;
 };
 
+// Records the calling thread's last error text and returns `code`.
+int set_last_error(int code, const char *message);
+
 cudaError_t launch_simt(const LinearProblem &pr, cudaStream_t stream);
 
 // Streaming kernels for m <= 16 (2-D problems, K-contiguous operands).

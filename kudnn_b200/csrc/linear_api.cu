@@ -84,6 +84,16 @@ struct DeviceBuffer {
 
 }  // namespace
 
+namespace kb {
+
+// Lets the other translation units of the library report through kudnn_b200_last_error().
+int set_last_error(int code, const char *message)
+{
+    return fail(code, "%s", message);
+}
+
+}  // namespace kb
+
 struct kudnn_b200_linear_s {
     kudnn_b200_linear_desc d;
     int forced_kernel = KUDNN_B200_KERNEL_AUTO;

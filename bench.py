@@ -42,7 +42,14 @@ WORKLOADS = {
 }
 
 # DRAM bytes per launch of the dominant kernel, from the ncu captures summarised under profiles/ (null until captured)
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/tc_linear_bf16_silu_m2048_n11008_k4096.md: 107.6 MB read + 21.2 MB written at m=2048; x and y scale with
+    # the rows, W does not, and the part of y still in L2 at kernel end is counted as written
+    "c2": 124.4e6 + 90.2e6,
+    # profiles/gemv_decode_bf16_n8192_k8192.md: traffic equals the algorithmic bytes within 0.1 % (+3 % for the m=16
+    # partial sums); scaled to n=28672 by the rows
+    "c4": 471.9e6 + 11.5e6,
+}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -299,6 +306,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5m", "c5n"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=0, help="override the row count (c4: 1, 4 or 16)")
+    ap.add_argument("--n", type=int, default=0, help="override the column count (smaller cases for profiler captures)")
+    ap.add_argument("--k", type=int, default=0, help="override the contraction length")
     ap.add_argument("--no-extras", action="store_true", help="skip the decode-GEMV, e2e and CPU legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -310,6 +319,12 @@ def main():
     w = dict(WORKLOADS["c5" if wname.startswith("c5") else wname])
     if args.m:
         w["m"] = args.m
+    if args.n:
+        w["n"] = args.n
+    if args.k:
+        w["k"] = args.k
+    if args.m or args.n or args.k:
+        w["label"] += " [overridden: m=%d n=%d k=%d]" % (w["m"], w["n"], w["k"])
 
     if args.impl == "reference":
         run_reference_arm(args, w, wname, rank)
@@ -355,7 +370,7 @@ def main():
 
     gathered = None
     if wname == "c5n" and world > 1:
-        gathered = torch.empty(world, m_local, n_local, device=device, dtype=tdt)
+        gathered = torch.empty(world * m_local, n_local, device=device, dtype=tdt)
         y_full = torch.empty(m_local, n_total, device=device, dtype=tdt)
 
     launches = [0]
@@ -368,7 +383,7 @@ def main():
         launches[0] += lin.last_launches
         if gathered is not None:
             dist.all_gather_into_tensor(gathered, y)
-            y_full.view(m_local, world, n_local).copy_(gathered.permute(1, 0, 2))
+            y_full.view(m_local, world, n_local).copy_(gathered.view(world, m_local, n_local).permute(1, 0, 2))
 
     sampler = ClockSampler(local_rank)
     sampler.start()

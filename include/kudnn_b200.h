@@ -125,6 +125,12 @@ KUDNN_B200_API int kudnn_b200_linear_run(kudnn_b200_linear_t handle, const kudnn
  * outputs back and synchronises.  A weight pointer that was pre-packed is not copied again. */
 KUDNN_B200_API int kudnn_b200_linear_run_host(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args);
 
+/* Looks at where args->a lives and calls kudnn_b200_linear_run (device memory) or kudnn_b200_linear_run_host (anything
+ * else).  All pointers of one call must be of the same kind.  This is what the C++ classes' Run methods use, so that
+ * code written for the reference (host pointers) and GPU-resident callers share one signature. */
+KUDNN_B200_API int kudnn_b200_linear_run_any(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args,
+                                             void *cuda_stream);
+
 /* Decode-shaped Linear (m <= 16, 2-D, K-contiguous a and b) that allocates no device memory, for callers that
  * cannot call cudaMalloc when they need the result: engines that have already handed all of HBM to their own pools,
  * plug-ins whose host forbids allocation inside an operator call, decode loops that cannot risk the device

@@ -57,7 +57,7 @@ class LinearArgs(ctypes.Structure):
 EXPORTS = [
     "kudnn_b200_linear_validate", "kudnn_b200_linear_create", "kudnn_b200_linear_clone", "kudnn_b200_linear_destroy",
     "kudnn_b200_linear_prepack", "kudnn_b200_linear_run", "kudnn_b200_linear_run_host", "kudnn_b200_linear_check",
-    "kudnn_b200_linear_run_static_scratch",
+    "kudnn_b200_linear_run_static_scratch", "kudnn_b200_linear_run_any",
     "kudnn_b200_linear_force_kernel", "kudnn_b200_linear_last_kernel", "kudnn_b200_linear_last_launches",
     "kudnn_b200_linear_workspace_bytes", "kudnn_b200_shard_range", "kudnn_b200_last_error", "kudnn_b200_version",
     "kudnn_b200_device_count",
@@ -89,6 +89,7 @@ def library():
     lib.kudnn_b200_linear_run.argtypes = [vp, ctypes.POINTER(LinearArgs), vp]
     lib.kudnn_b200_linear_run_host.argtypes = [vp, ctypes.POINTER(LinearArgs)]
     lib.kudnn_b200_linear_check.argtypes = [vp, vp]
+    lib.kudnn_b200_linear_run_any.argtypes = [vp, ctypes.POINTER(LinearArgs), vp]
     lib.kudnn_b200_linear_run_static_scratch.argtypes = [ctypes.POINTER(LinearDesc), ctypes.POINTER(LinearArgs), vp]
     lib.kudnn_b200_linear_force_kernel.argtypes = [vp, i32]
     lib.kudnn_b200_linear_last_kernel.argtypes = [vp]

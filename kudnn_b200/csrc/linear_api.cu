@@ -770,6 +770,22 @@ int kudnn_b200_linear_run_host(kudnn_b200_linear_t h, const kudnn_b200_linear_ar
     return KUDNN_B200_OK;
 }
 
+int kudnn_b200_linear_run_any(kudnn_b200_linear_t h, const kudnn_b200_linear_args *args, void *cuda_stream)
+{
+    if (h == nullptr || args == nullptr || args->a == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run: null argument");
+    }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, args->a) != cudaSuccess) {
+        (void)cudaGetLastError();
+        attr.type = cudaMemoryTypeUnregistered;
+    }
+    if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) {
+        return kudnn_b200_linear_run(h, args, cuda_stream);
+    }
+    return kudnn_b200_linear_run_host(h, args);
+}
+
 int kudnn_b200_linear_check(kudnn_b200_linear_t h, void *cuda_stream)
 {
     if (h == nullptr) {

@@ -20,6 +20,7 @@
 #include <cstddef>
 #include <cstdint>
 #include <initializer_list>
+#include <iterator>
 #include <limits>
 #include <memory>
 #include <new>
@@ -202,10 +203,10 @@ struct Shape final {
         ResetShape(ptr, size);
     }
     // the variadic form also enforces the reference's 3 GiB-per-tensor guard (elements * 4 bytes)
-    template <typename... Ts>
+    template <typename... Ts, typename = typename std::enable_if<(sizeof...(Ts) > 0) &&
+                                                                 (std::is_arithmetic<Ts>::value && ...)>::type>
     Shape(Ts... dims) noexcept(false) : dimsArray{{static_cast<SizeType>(dims)...}}, numDims{sizeof...(dims)}
     {
-        static_assert(sizeof...(dims) > 0, "use the default constructor for an empty shape");
         CheckRank(numDims);
         const long long total = static_cast<long long>(GetTotalDimsSize());
         if (total * 4 > 3LL * 1024 * 1024 * 1024) {
@@ -214,7 +215,7 @@ struct Shape final {
     }
     Shape(const std::initializer_list<SizeType> &list) noexcept(false) : dimsArray{}, numDims{0} { ResetShape(list); }
 
-    template <typename... Ts>
+    template <typename... Ts, typename = typename std::enable_if<(std::is_arithmetic<Ts>::value && ...)>::type>
     Shape &ResetShape(Ts... dims) noexcept(false)
     {
         CheckRank(sizeof...(dims));

@@ -199,8 +199,14 @@ class CpuArm:
             lib = ko.load()
             self.build = "-march=x86-64-v3 (prebuilt)"
         self.lib = lib
+        if threads <= 0:
+            # all cores this process may use; launchers such as torch.distributed.run export OMP_NUM_THREADS=1
+            try:
+                threads = len(os.sched_getaffinity(0))
+            except AttributeError:
+                threads = os.cpu_count() or 1
         self.threads = threads
-        self.cores = lib.ko_num_threads() if threads <= 0 else threads
+        self.cores = threads
         self.code = {"f32": ko.F32, "f16": ko.F16, "bf16": ko.BF16}[w["dtype"]]
         self.act = {None: ko.ACT_NONE, "relu": ko.ACT_RELU, "silu": ko.ACT_SWISH, "gelu_tanh": ko.ACT_GELU_TANH}[w["act"]]
         self.res_op = {None: ko.RES_NONE, "add": ko.RES_IDENTICAL, "mul": ko.RES_ELTWISE_MUL}[w["res"]]

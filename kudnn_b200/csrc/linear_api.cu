@@ -120,7 +120,14 @@ struct kudnn_b200_linear_s {
     // tensor-map cache of the last tensor-core launch
     kb::TcPlan tc_plan;
     const void *plan_a = nullptr, *plan_b = nullptr;
+    long long plan_m = 0;
     bool plan_valid = false;
+
+    // host-pointer path: copy-in, compute and copy-out streams with one event pair per row chunk
+    static constexpr int kMaxChunks = 16;
+    bool pipe_ready = false;
+    cudaStream_t pipe_stream[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t pipe_in[kMaxChunks], pipe_done[kMaxChunks];
 };
 
 namespace {
@@ -285,9 +292,9 @@ int pack_weights(Handle *h, const void *b_dev, DeviceBuffer *buf, bool with_raw,
     return KUDNN_B200_OK;
 }
 
-int run_device(Handle *h, const kudnn_b200_linear_args &args, cudaStream_t stream)
+// `d` is the handle's descriptor, or a copy of it restricted to a block of rows (host-pointer pipeline)
+int run_device(Handle *h, const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &args, cudaStream_t stream)
 {
-    const kudnn_b200_linear_desc &d = h->d;
     if (args.a == nullptr || args.b == nullptr) {
         return fail(KUDNN_B200_BAD_ARGUMENTS, "run: a and b must not be null");
     }
@@ -428,13 +435,14 @@ int run_device(Handle *h, const kudnn_b200_linear_args &args, cudaStream_t strea
                 ops.a = h->a_scratch.ptr;
                 ops.lda = k_pad;
             }
-            if (!(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b)) {
+            if (!(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b && h->plan_m == d.m)) {
                 cudaError_t e = kb::tc_make_plan(ops, d.m, d.n, h->sm_count, &h->tc_plan);
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "tensor map encoding");
                 }
                 h->plan_a = ops.a;
                 h->plan_b = ops.b;
+                h->plan_m = d.m;
                 h->plan_valid = true;
             }
             cudaError_t e = kb::launch_tc(ops, h->tc_plan, pr.epi, d.m, d.n,
@@ -461,6 +469,165 @@ int run_device(Handle *h, const kudnn_b200_linear_args &args, cudaStream_t strea
     h->last_kernel = KUDNN_B200_KERNEL_SIMT;
     h->last_launches = 1;
     return KUDNN_B200_OK;
+}
+
+// Host-pointer execution of a large 2-D problem as a pipeline over blocks of rows: while block i is computed, block
+// i+1 is copied in and block i-1 is copied out, each on its own stream, so a call costs about the slowest of the
+// three instead of their sum.  Rows of a, c, res and out must be contiguous along their second dimension.
+bool pipeline_applies(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &args)
+{
+    if (batch_extent(d, 0) * batch_extent(d, 1) * batch_extent(d, 2) != 1 || d.m < 1024 || args.beta != 0.0f) {
+        return false;
+    }
+    if (d.a_sk != 1 || d.a_sm < d.k || d.c_sn != 1 || d.c_sm < d.n) {
+        return false;
+    }
+    if (d.res_op != KUDNN_B200_RES_NONE && (d.res_sn != 1 || d.res_sm < d.n || d.out_sn != 1 || d.out_sm < d.n)) {
+        return false;
+    }
+    if (d.has_bias && d.bias_sm != 0 && (d.bias_sn != 1 || d.bias_sm < d.n)) {
+        return false;
+    }
+    const char *off = std::getenv("KUDNN_B200_HOST_PIPELINE");
+    return !(off != nullptr && std::strcmp(off, "0") == 0);
+}
+
+int ensure_pipeline(Handle *h)
+{
+    if (h->pipe_ready) {
+        return KUDNN_B200_OK;
+    }
+    for (auto &st : h->pipe_stream) {
+        cudaError_t e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "host pipeline streams");
+        }
+    }
+    for (int i = 0; i < Handle::kMaxChunks; ++i) {
+        cudaError_t e = cudaEventCreateWithFlags(&h->pipe_in[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) {
+            e = cudaEventCreateWithFlags(&h->pipe_done[i], cudaEventDisableTiming);
+        }
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "host pipeline events");
+        }
+    }
+    h->pipe_ready = true;
+    return KUDNN_B200_OK;
+}
+
+int read_status(Handle *h)
+{
+    kb::DeviceStatus st;
+    cudaError_t e = cudaMemcpy(&st, h->status.ptr, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "status read");
+    }
+    if (st.code != kb::kErrNone) {
+        cudaMemset(h->status.ptr, 0, sizeof(st));
+        return fail(KUDNN_B200_TIMEOUT, "device-side wait gave up (site %d, block %d)", st.where, st.block);
+    }
+    return KUDNN_B200_OK;
+}
+
+int run_host_pipelined(Handle *h, const kudnn_b200_linear_args &args)
+{
+    const kudnn_b200_linear_desc &d = h->d;
+    int rc = ensure_pipeline(h);
+    if (rc != KUDNN_B200_OK) {
+        return rc;
+    }
+    cudaStream_t s_in = h->pipe_stream[0], s_run = h->pipe_stream[1], s_out = h->pipe_stream[2];
+    const bool has_res = d.res_op != KUDNN_B200_RES_NONE;
+    const size_t es_a = kb::dtype_size(d.a_dtype), es_c = kb::dtype_size(d.c_dtype);
+    const size_t es_bias = kb::dtype_size(d.bias_dtype), es_res = kb::dtype_size(d.res_dtype), es_out = kb::dtype_size(d.out_dtype);
+    const size_t bytes_a = (static_cast<size_t>(d.m - 1) * d.a_sm + d.k) * es_a;
+    const size_t bytes_c = (static_cast<size_t>(d.m - 1) * d.c_sm + d.n) * es_c;
+    const size_t bytes_b = static_cast<size_t>(span_elems(d.k, d.b_sk, d.n, d.b_sn, d, d.b_sb)) * kb::dtype_size(d.b_dtype);
+    const size_t bytes_bias = d.has_bias ? static_cast<size_t>(span_elems(d.m, d.bias_sm, d.n, d.bias_sn, d, d.bias_sb)) * es_bias : 0;
+    const size_t bytes_res = has_res ? (static_cast<size_t>(d.m - 1) * d.res_sm + d.n) * es_res : 0;
+    const size_t bytes_out = has_res ? (static_cast<size_t>(d.m - 1) * d.out_sm + d.n) * es_out : 0;
+    cudaError_t e = h->stage[0].reserve(bytes_a);
+    if (e == cudaSuccess && args.c != nullptr) e = h->stage[2].reserve(bytes_c);
+    if (e == cudaSuccess && d.has_bias) e = h->stage[3].reserve(bytes_bias);
+    if (e == cudaSuccess && has_res) e = h->stage[4].reserve(bytes_res);
+    if (e == cudaSuccess && has_res) e = h->stage[5].reserve(bytes_out);
+    const bool b_cached = (h->packed_key != nullptr && h->packed_key == args.b);
+    if (e == cudaSuccess && !b_cached) e = h->stage[1].reserve(bytes_b);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "host staging");
+    }
+    char *dev_a = static_cast<char *>(h->stage[0].ptr), *dev_c = static_cast<char *>(h->stage[2].ptr);
+    char *dev_bias = static_cast<char *>(h->stage[3].ptr), *dev_res = static_cast<char *>(h->stage[4].ptr);
+    char *dev_out = static_cast<char *>(h->stage[5].ptr);
+    if (!b_cached) {
+        e = cudaMemcpyAsync(h->stage[1].ptr, args.b, bytes_b, cudaMemcpyHostToDevice, s_in);
+    }
+    if (e == cudaSuccess && d.has_bias) {
+        e = cudaMemcpyAsync(dev_bias, args.bias, bytes_bias, cudaMemcpyHostToDevice, s_in);
+    }
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "host to device copy");
+    }
+    long long rows = (d.m + 7) / 8;
+    rows = std::max<long long>((rows + 127) / 128 * 128, 256);
+    const int chunks = static_cast<int>((d.m + rows - 1) / rows);
+    int launches = 0;
+    for (int i = 0; i < chunks && i < Handle::kMaxChunks; ++i) {
+        const long long r0 = i * rows, nr = std::min<long long>(rows, d.m - r0);
+        const size_t off_a = static_cast<size_t>(r0) * d.a_sm * es_a;
+        e = cudaMemcpyAsync(dev_a + off_a, static_cast<const char *>(args.a) + off_a,
+                            (static_cast<size_t>(nr - 1) * d.a_sm + d.k) * es_a, cudaMemcpyHostToDevice, s_in);
+        if (e == cudaSuccess && has_res) {
+            const size_t off = static_cast<size_t>(r0) * d.res_sm * es_res;
+            e = cudaMemcpyAsync(dev_res + off, static_cast<const char *>(args.res) + off,
+                                (static_cast<size_t>(nr - 1) * d.res_sm + d.n) * es_res, cudaMemcpyHostToDevice, s_in);
+        }
+        if (e == cudaSuccess) e = cudaEventRecord(h->pipe_in[i], s_in);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s_run, h->pipe_in[i], 0);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "host pipeline copy-in");
+        }
+        kudnn_b200_linear_desc sub = d;
+        sub.m = nr;
+        kudnn_b200_linear_args dev = args;
+        dev.a = dev_a + off_a;
+        dev.b = b_cached ? args.b : h->stage[1].ptr;
+        dev.c = args.c != nullptr ? dev_c + static_cast<size_t>(r0) * d.c_sm * es_c : nullptr;
+        dev.bias = d.has_bias ? dev_bias + static_cast<size_t>(r0) * d.bias_sm * es_bias : nullptr;
+        dev.res = has_res ? dev_res + static_cast<size_t>(r0) * d.res_sm * es_res : nullptr;
+        dev.out = has_res ? dev_out + static_cast<size_t>(r0) * d.out_sm * es_out : nullptr;
+        rc = run_device(h, sub, dev, s_run);
+        if (rc != KUDNN_B200_OK) {
+            cudaDeviceSynchronize();
+            return rc;
+        }
+        launches += h->last_launches;
+        e = cudaEventRecord(h->pipe_done[i], s_run);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s_out, h->pipe_done[i], 0);
+        if (e == cudaSuccess && args.c != nullptr) {
+            const size_t off = static_cast<size_t>(r0) * d.c_sm * es_c;
+            e = cudaMemcpyAsync(static_cast<char *>(args.c) + off, dev_c + off, (static_cast<size_t>(nr - 1) * d.c_sm + d.n) * es_c,
+                                cudaMemcpyDeviceToHost, s_out);
+        }
+        if (e == cudaSuccess && has_res) {
+            const size_t off = static_cast<size_t>(r0) * d.out_sm * es_out;
+            e = cudaMemcpyAsync(static_cast<char *>(args.out) + off, dev_out + off,
+                                (static_cast<size_t>(nr - 1) * d.out_sm + d.n) * es_out, cudaMemcpyDeviceToHost, s_out);
+        }
+        if (e != cudaSuccess) {
+            cudaDeviceSynchronize();
+            return fail_cuda(e, "host pipeline copy-out");
+        }
+    }
+    h->last_launches = launches;
+    e = cudaStreamSynchronize(s_out);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s_run);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s_in);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "run_host");
+    }
+    return read_status(h);
 }
 
 }  // namespace
@@ -588,6 +755,15 @@ int kudnn_b200_linear_destroy(kudnn_b200_linear_t h)
         for (auto &s : h->stage) {
             s.release();
         }
+        if (h->pipe_ready) {
+            for (auto &st : h->pipe_stream) {
+                cudaStreamDestroy(st);
+            }
+            for (int i = 0; i < kudnn_b200_linear_s::kMaxChunks; ++i) {
+                cudaEventDestroy(h->pipe_in[i]);
+                cudaEventDestroy(h->pipe_done[i]);
+            }
+        }
         if (cur >= 0) {
             cudaSetDevice(cur);
         }
@@ -654,11 +830,10 @@ int kudnn_b200_linear_prepack(kudnn_b200_linear_t h, const void *b, void *cuda_s
         h->packed_ktotal = kt;
     }
     h->packed_key = b;
-    if (!on_device) {
-        e = cudaStreamSynchronize(stream);  // the staging buffer is reused by later host runs
-        if (e != cudaSuccess) {
-            return fail_cuda(e, "prepack");
-        }
+    // one-time cost: later runs may use other streams (the host-pointer pipeline does) and the staging buffer is reused
+    e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "prepack");
     }
     return KUDNN_B200_OK;
 }
@@ -669,7 +844,7 @@ int kudnn_b200_linear_run(kudnn_b200_linear_t h, const kudnn_b200_linear_args *a
         return fail(KUDNN_B200_BAD_ARGUMENTS, "run: null argument");
     }
     std::lock_guard<std::mutex> guard(h->lock);
-    return run_device(h, *args, static_cast<cudaStream_t>(cuda_stream));
+    return run_device(h, h->d, *args, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int kudnn_b200_linear_run_host(kudnn_b200_linear_t h, const kudnn_b200_linear_args *args)
@@ -694,6 +869,9 @@ int kudnn_b200_linear_run_host(kudnn_b200_linear_t h, const kudnn_b200_linear_ar
     }
     if (d.res_op == KUDNN_B200_RES_NONE && args->c == nullptr) {
         return fail(KUDNN_B200_BAD_ARGUMENTS, "run_host: c must not be null");
+    }
+    if (pipeline_applies(d, *args)) {
+        return run_host_pipelined(h, *args);
     }
     cudaStream_t stream = nullptr;
     const size_t bytes_a = static_cast<size_t>(span_elems(d.m, d.a_sm, d.k, d.a_sk, d, d.a_sb)) * kb::dtype_size(d.a_dtype);
@@ -742,7 +920,7 @@ int kudnn_b200_linear_run_host(kudnn_b200_linear_t h, const kudnn_b200_linear_ar
         }
     }
 #undef KB_STAGE_IN
-    rc = run_device(h, dev, stream);
+    rc = run_device(h, d, dev, stream);
     if (rc != KUDNN_B200_OK) {
         return rc;
     }

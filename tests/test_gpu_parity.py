@@ -187,7 +187,7 @@ def test_golden_vectors(cuda_device, name, kernel):
 
 
 @pytest.mark.parametrize("dtype,m,n,k", [("f32", 128, 1024, 1024), ("bf16", 256, 512, 512), ("bf16", 4, 512, 1024),
-                                          ("f16", 33, 47, 20)])
+                                          ("f16", 33, 47, 20), ("bf16", 1500, 520, 264), ("f32", 1100, 300, 72)])
 @pytest.mark.parametrize("prepack", [False, True])
 def test_host_pointer_path(cuda_device, dtype, m, n, k, prepack):
     case = dict(m=m, n=n, k=k, dtype=dtype, bias="row", act=kb.ACT_RELU, act_alpha=0.0, res_op=kb.RES_IDENTICAL,

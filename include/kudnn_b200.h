@@ -64,6 +64,7 @@ extern "C" {
 #define KUDNN_B200_KERNEL_GEMV_FMA 2 /* m <= 4 streaming kernel, fp32 FMA + warp-shuffle reduction */
 #define KUDNN_B200_KERNEL_GEMV_MMA 3 /* m <= 16 streaming kernel, 16-bit inputs */
 #define KUDNN_B200_KERNEL_TC 4       /* tcgen05 / TMEM tensor-core kernel fed by TMA */
+#define KUDNN_B200_KERNEL_GEMV_RING 5 /* m <= 16 streaming kernel, weights through a bulk-copy shared-memory ring */
 
 /* Replaces the argument lists of the reference constructors:
  *   Gemm(aInfo,bInfo,cInfo,biasInfo,numThreads)                     src/dnn/include/operations/kudnn_gemm.hpp:36-39

@@ -9,8 +9,8 @@ import os
 F32, F16, BF16 = 1, 2, 3
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_SIGMOID, ACT_GELU_TANH, ACT_SWISH, ACT_GELU_ERF = 0, 5, 9, 10, 20, 25, 27
 RES_NONE, RES_EXT, RES_IDENTICAL, RES_ELTWISE_MUL = 0, 1, 2, 3
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_TC = 0, 1, 2, 3, 4
-KERNEL_NAMES = {0: "auto", 1: "simt", 2: "gemv_fma", 3: "gemv_mma", 4: "tc"}
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_TC, KERNEL_GEMV_RING = 0, 1, 2, 3, 4, 5
+KERNEL_NAMES = {0: "auto", 1: "simt", 2: "gemv_fma", 3: "gemv_mma", 4: "tc", 5: "gemv_ring"}
 
 STATUS_NAMES = {0: "OK", 1: "UNSUPPORTED", 2: "BAD_ARGUMENTS", 3: "ALLOC_FAILED", 4: "CUDA_ERROR", 5: "TIMEOUT",
                 6: "NO_DEVICE"}

@@ -102,16 +102,15 @@ __device__ __forceinline__ void store_exact(void *p, int dtype, long long idx, f
     }
 }
 
-// 1 / (1 + exp(t)) with the reference's clamp of the exponent argument to [-87, 87]
-// (src/dnn/src/kernels/vml/vml_sve_la_sigmoid.h:39-48).  Written without branches: the epilogues evaluate eight of
-// these side by side and rely on the compiler interleaving them.
+// 1 / (1 + exp(t)); the reference clamps the exponent argument to [-87, 87]
+// (src/dnn/src/kernels/vml/vml_sve_la_sigmoid.h:39-48).
 template <bool kPrecise>
 __device__ __forceinline__ float sigmoid_neg(float t)
 {
-    const float tc = fminf(fmaxf(t, -87.0f), 87.0f);
-    const float s = kPrecise ? (1.0f / (1.0f + expf(tc))) : __fdividef(1.0f, 1.0f + __expf(tc));
-    const float hi = (t > 87.0f) ? 0.0f : s;
-    return (t < -87.0f) ? 1.0f : hi;
+    // No explicit clamp is needed: beyond +87 the exponential overflows to +inf and the quotient is 0, beyond -87 it
+    // underflows and the quotient is 1, which are the reference's clamped values (a denormal instead of 0 in the
+    // sliver 87 < t < 88.7).  Branch-free, so eight of these interleave in the epilogues.
+    return kPrecise ? (1.0f / (1.0f + expf(t))) : __fdividef(1.0f, 1.0f + __expf(t));
 }
 
 // kPrecise selects libm-grade exp/erf (fp32 outputs); otherwise the fast hardware approximations, whose error

@@ -233,6 +233,65 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], unsigned a0, unsigned a
     }
 }
 
+// Ends a warp's work on one group of 8 weight rows.  The lane holds y[gid][n0 + 2*tig + {0,1}] in acc[0..1] and
+// y[gid + 8][...] in acc[2..3].  A group that one warp covered alone goes straight to the epilogue; otherwise the
+// partial tile goes to the warp's slot and the last arrival adds all slots in slot order.
+__device__ __forceinline__ void mma_finish_group(const GemvParams &p, float (&acc)[4], long long group, int chunk, int warp,
+                                                 int lane)
+{
+    const int gid = lane >> 2, tig = lane & 3;
+    const long long n0 = group * 8 + tig * 2;
+    const long long first_blk = group * p.kb;
+    const int w0 = static_cast<int>(first_blk / p.span);
+    const int w1 = static_cast<int>((first_blk + p.kb - 1) / p.span);
+    const int pieces = w1 - w0 + 1;
+    const bool whole = (p.ksplit == 1) && (pieces == 1);
+    bool finish = whole;
+    if (!whole) {
+        const int slot = chunk * p.slots + (warp - w0);
+        float *unit = p.partials + group * (static_cast<long long>(p.ksplit) * p.slots * 128);
+        *reinterpret_cast<float4 *>(unit + slot * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        __threadfence();
+        __syncwarp();
+        unsigned old = 0u;
+        if (lane == 0) {
+            old = atomicAdd(p.counters + group, 1u);
+        }
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == static_cast<unsigned>(p.ksplit * pieces - 1)) {
+            __threadfence();
+            float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int c = 0; c < p.ksplit; ++c) {
+                for (int j = 0; j < pieces; ++j) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(unit + (c * p.slots + j) * 128 + lane * 4));
+                    s[0] += v.x;
+                    s[1] += v.y;
+                    s[2] += v.z;
+                    s[3] += v.w;
+                }
+            }
+            acc[0] = s[0];
+            acc[1] = s[1];
+            acc[2] = s[2];
+            acc[3] = s[3];
+            finish = true;
+            if (lane == 0) {
+                p.counters[group] = 0u;
+            }
+        }
+    }
+    if (finish) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int mi = gid + ((e >= 2) ? 8 : 0);
+            const long long ni = n0 + (e & 1);
+            if (mi < p.m && ni < p.n) {
+                epilogue_scalar(p.epi, acc[e], mi, ni);
+            }
+        }
+    }
+}
+
 // kRows16: activations occupy both 8-row halves of the 16-row operand (m > 8)
 template <int kDtype, bool kRows16, int kUnroll, int kThreads, int kMinBlocks>
 __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_mma_kernel(const GemvParams p)
@@ -306,58 +365,201 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_mma_kernel(const Ge
             }
         }
 
-        // lane holds y[gid][n0 + 2*tig + {0,1}] in acc[0..1] and y[gid + 8][...] in acc[2..3]
-        const long long n0 = group * 8 + tig * 2;
-        const long long first_blk = group * p.kb;
-        const int w0 = static_cast<int>(first_blk / p.span);
-        const int w1 = static_cast<int>((first_blk + p.kb - 1) / p.span);
-        const int pieces = w1 - w0 + 1;
-        const bool whole = (p.ksplit == 1) && (pieces == 1);
-        bool finish = whole;
-        if (!whole) {
-            const int slot = chunk * p.slots + (warp - w0);
-            float *unit = p.partials + group * (static_cast<long long>(p.ksplit) * p.slots * 128);
-            *reinterpret_cast<float4 *>(unit + slot * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            __threadfence();
-            __syncwarp();
-            unsigned old = 0u;
-            if (lane == 0) {
-                old = atomicAdd(p.counters + group, 1u);
+        mma_finish_group(p, acc, group, chunk, warp, lane);
+        f += nb;
+    }
+}
+
+// ------------------------------------------------------------------------------- MMA kernel, staged weight feed
+//
+// Same arithmetic and the same work decomposition as gemv_mma_kernel, with a block of 8 rows x 256 k.  What changes is
+// how the weights reach the fragment layout.  HBM delivers about 12 % more for loads in which a warp reads 512
+// consecutive bytes of one row than for the 8 rows x 64 bytes a fragment-shaped load touches, so here every load
+// instruction reads one row segment; the 8 segments of a block go through 4 KiB of shared memory that belongs to
+// the warp alone (no CTA-wide barrier anywhere in the loop) and come back in fragment layout through ldmatrix.  The
+// loads of the next block are issued before the current one is staged, so a warp always has 4 KiB in flight.
+// ldmatrix hands thread (gid, tig) of matrix j the elements k = 8j + 2*tig, +1 of row gid; the activations are
+// stored in shared memory with the words of every 32-k block transposed 4 x 4 so that the four words a thread needs
+// for the two MMAs of that block are one 16-byte load.
+constexpr int kStagedThreads = 512;
+constexpr int kStagedBlockK = 256;
+constexpr int kStagedPitch = kStagedBlockK * 2 + 16;  // bytes per staged row; the skew spreads the 8 rows over the banks
+constexpr int kStagedWarpBytes = 8 * kStagedPitch;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+template <int kDtype, bool kRows16>
+__global__ void __launch_bounds__(kStagedThreads, 1) gemv_mma_staged_kernel(const GemvParams p)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int kRows = kRows16 ? 16 : 8;
+    const int row_bytes = p.kc * 2 + kMmaRowPadBytes;
+    const int chunk = blockIdx.x % p.ksplit;
+    const int cta_in_chunk = blockIdx.x / p.ksplit;
+    const int kc0 = chunk * p.kc;
+
+    const int lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int warp_in_cta = threadIdx.x >> 5;
+    const int warp = cta_in_chunk * (kStagedThreads / 32) + warp_in_cta;
+    const bool active = warp < p.active_warps;
+    long long f = static_cast<long long>(warp) * p.span;
+    const long long f_end = (f + p.span < p.total) ? f + p.span : p.total;
+    const unsigned short *wg = static_cast<const unsigned short *>(p.w);
+    const int k_end = (kc0 + p.kc < p.k) ? kc0 + p.kc : p.k;
+
+    // rows [row0, row0 + rows_ok) of the weights, block blk of this chunk: one 512-byte row segment per instruction
+    auto load_block = [&](uint4 (&v)[8], long long row0, int rows_ok, int blk) {
+        const int kloc = blk * kStagedBlockK;
+        const bool k_ok = kc0 + kloc + lane * 8 < k_end;
+        const unsigned short *src = wg + row0 * p.w_ld + kc0 + kloc + lane * 8;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            v[r] = make_uint4(0u, 0u, 0u, 0u);
+            if (k_ok && r < rows_ok) {
+                v[r] = ld_stream_16(src + r * p.w_ld);
             }
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old == static_cast<unsigned>(p.ksplit * pieces - 1)) {
-                __threadfence();
-                float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                for (int c = 0; c < p.ksplit; ++c) {
-                    for (int j = 0; j < pieces; ++j) {
-                        const float4 v =
-                            __ldcg(reinterpret_cast<const float4 *>(unit + (c * p.slots + j) * 128 + lane * 4));
-                        s[0] += v.x;
-                        s[1] += v.y;
-                        s[2] += v.z;
-                        s[3] += v.w;
+        }
+    };
+    auto rows_of = [&](long long group) {
+        const long long left = p.n - group * 8;
+        return left >= 8 ? 8 : static_cast<int>(left);
+    };
+
+    // the first weight block is requested before anything else, so HBM is already busy while the activations load
+    uint4 va[8], vb[8];
+    if (active && f < f_end) {
+        const long long group = f / p.kb;
+        load_block(va, group * 8, rows_of(group), static_cast<int>(f - group * p.kb));
+    }
+
+    // Activations of this chunk -> shared memory.  Every thread issues eight 16-byte loads before it stores anything
+    // (one round trip to L2 per eight vectors).  The 16 words of a 32-k block are stored transposed 4 x 4: vector q
+    // of a block supplies word q of each of the block's four 16-byte groups.  Which group a lane writes first is
+    // rotated with the block index, which keeps the 32 lanes of a store on distinct banks.
+    {
+        const int vec_per_row = p.kc / 8;
+        const int total_vec = kRows * vec_per_row;
+        const unsigned short *xg = static_cast<const unsigned short *>(p.x);
+        for (int base = threadIdx.x; base < total_vec; base += kStagedThreads * 8) {
+            uint4 xv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * kStagedThreads;
+                xv[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (i < total_vec) {
+                    const int mi = i / vec_per_row, vi = i - mi * vec_per_row;
+                    const int kk = kc0 + vi * 8;
+                    if (mi < p.m && kk < p.k) {
+                        xv[u] = *reinterpret_cast<const uint4 *>(xg + static_cast<long long>(mi) * p.x_ld + kk);
                     }
                 }
-                acc[0] = s[0];
-                acc[1] = s[1];
-                acc[2] = s[2];
-                acc[3] = s[3];
-                finish = true;
-                if (lane == 0) {
-                    p.counters[group] = 0u;
-                }
             }
-        }
-        if (finish) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int mi = gid + ((e >= 2) ? 8 : 0);
-                const long long ni = n0 + (e & 1);
-                if (mi < p.m && ni < p.n) {
-                    epilogue_scalar(p.epi, acc[e], mi, ni);
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * kStagedThreads;
+                if (i < total_vec) {
+                    const int mi = i / vec_per_row, vi = i - mi * vec_per_row;
+                    const int blk = vi >> 2, q = vi & 3;
+                    const int rot = (blk >> 1) & 3;
+                    // c[t] = component (t + rot) & 3 of the vector
+                    unsigned c0 = xv[u].x, c1 = xv[u].y, c2 = xv[u].z, c3 = xv[u].w;
+                    if (rot & 1) {
+                        const unsigned tmp = c0;
+                        c0 = c1;
+                        c1 = c2;
+                        c2 = c3;
+                        c3 = tmp;
+                    }
+                    if (rot & 2) {
+                        unsigned tmp = c0;
+                        c0 = c2;
+                        c2 = tmp;
+                        tmp = c1;
+                        c1 = c3;
+                        c3 = tmp;
+                    }
+                    unsigned *dst = reinterpret_cast<unsigned *>(smem_raw + mi * row_bytes) + (blk << 4) + q;
+                    dst[((0 + rot) & 3) << 2] = c0;
+                    dst[((1 + rot) & 3) << 2] = c1;
+                    dst[((2 + rot) & 3) << 2] = c2;
+                    dst[((3 + rot) & 3) << 2] = c3;
                 }
             }
         }
+    }
+    __syncthreads();
+    if (!active) {
+        return;
+    }
+
+    const unsigned char *xa_row = smem_raw + gid * row_bytes + tig * 16;
+    const unsigned char *xb_row = smem_raw + (gid + 8) * row_bytes + tig * 16;
+    unsigned char *stage = smem_raw + kRows * row_bytes + warp_in_cta * kStagedWarpBytes;
+    const uint32_t stage_st = static_cast<uint32_t>(__cvta_generic_to_shared(stage)) + static_cast<uint32_t>(lane * 16);
+    const uint32_t stage_ld = static_cast<uint32_t>(__cvta_generic_to_shared(stage)) +
+                              static_cast<uint32_t>((lane & 7) * kStagedPitch + (lane >> 3) * 16);
+    bool preloaded = true;
+
+    while (f < f_end) {
+        const long long group = f / p.kb;
+        const int kb0 = static_cast<int>(f - group * p.kb);
+        const int nb = static_cast<int>(((p.kb - kb0) < (f_end - f)) ? (p.kb - kb0) : (f_end - f));
+        const long long row0 = group * 8;
+        const int rows_ok = rows_of(group);
+
+        float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        auto consume_block = [&](const uint4 (&v)[8], int blk) {
+            __syncwarp();  // the ldmatrix reads of the previous block are done
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_st + r * kStagedPitch), "r"(v[r].x),
+                             "r"(v[r].y), "r"(v[r].z), "r"(v[r].w)
+                             : "memory");
+            }
+            __syncwarp();
+            const int xoff = blk * kStagedBlockK * 2;
+#pragma unroll
+            for (int s = 0; s < kStagedBlockK / 32; ++s) {
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4(stage_ld + s * 64, b0, b1, b2, b3);
+                const uint4 xa = *reinterpret_cast<const uint4 *>(xa_row + xoff + s * 64);
+                uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+                if (kRows16) {
+                    xb = *reinterpret_cast<const uint4 *>(xb_row + xoff + s * 64);
+                }
+                mma_16816<kDtype>(acc0, xa.x, xb.x, xa.y, xb.y, b0, b1);
+                mma_16816<kDtype>(acc1, xa.z, xb.z, xa.w, xb.w, b2, b3);
+            }
+        };
+
+        if (!preloaded) {
+            load_block(va, row0, rows_ok, kb0);
+        }
+        preloaded = false;
+        for (int i = 0; i < nb; i += 2) {
+            if (i + 1 < nb) {
+                load_block(vb, row0, rows_ok, kb0 + i + 1);
+            }
+            consume_block(va, kb0 + i);
+            if (i + 1 < nb) {
+                if (i + 2 < nb) {
+                    load_block(va, row0, rows_ok, kb0 + i + 2);
+                }
+                consume_block(vb, kb0 + i + 1);
+            }
+        }
+        float acc[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            acc[e] = acc0[e] + acc1[e];
+        }
+        mma_finish_group(p, acc, group, chunk, warp, lane);
         f += nb;
     }
 }
@@ -420,11 +622,29 @@ cudaError_t launch_mma_rows(const GemvParams &p, const GemvPlan &plan, cudaStrea
     return cudaGetLastError();
 }
 
+template <int kDtype>
+cudaError_t launch_mma_staged(const GemvParams &p, const GemvPlan &plan, cudaStream_t stream)
+{
+    if (p.m > 8) {
+        auto kernel = gemv_mma_staged_kernel<kDtype, true>;
+        cudaError_t e = set_smem(kernel, plan.smem_bytes);
+        if (e != cudaSuccess) return e;
+        kernel<<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);
+    } else {
+        auto kernel = gemv_mma_staged_kernel<kDtype, false>;
+        cudaError_t e = set_smem(kernel, plan.smem_bytes);
+        if (e != cudaSuccess) return e;
+        kernel<<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);
+    }
+    return cudaGetLastError();
+}
+
 // Launch shapes: threads per CTA / resident CTAs per SM the kernel is compiled for.
 struct GemvShape {
     int threads, min_blocks;
 };
 constexpr GemvShape kShapes[3] = {{512, 2}, {1024, 1}, {1024, 2}};
+constexpr int kStagedShape = 3;  // GemvPlan::shape of the staged-feed MMA kernel
 
 template <int kDtype, bool kFma>
 cudaError_t launch_shape(const GemvParams &p, const GemvPlan &plan, int shape, int unroll, cudaStream_t stream)
@@ -517,6 +737,50 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
         return false;
     }
     const int rows = pr.m > 8 ? 16 : 8;
+    // The staged feed wins for up to 8 activation rows; with 16 rows the second half of the activation operand
+    // doubles the shared-memory reads per block and the fragment-shaped loads are faster (measured).  The
+    // environment switch forces one feed for every m (1) or turns the staged feed off (0).
+    const int staged_env = env_int("KUDNN_B200_GEMV_STAGED", -1);
+    const bool staged = staged_env < 0 ? rows == 8 : staged_env != 0;
+    if (staged && (shape < 0 || shape == kStagedShape)) {
+        // staged feed: 512 threads, one CTA per SM, blocks of 8 rows x 256 k
+        const int warps = kStagedThreads / 32;
+        const size_t staging = static_cast<size_t>(warps) * kStagedWarpBytes;
+        const size_t budget = 225 * 1024 - staging;
+        int ksplit = env_int("KUDNN_B200_GEMV_KSPLIT", 0);
+        auto chunk_len = [&](int parts) {
+            return ((pr.k + parts - 1) / parts + kStagedBlockK - 1) / kStagedBlockK * kStagedBlockK;
+        };
+        if (ksplit <= 0) {
+            ksplit = 1;
+            while (ksplit < 64 && static_cast<size_t>(rows) * (chunk_len(ksplit) * 2 + kMmaRowPadBytes) > budget) {
+                ksplit *= 2;
+            }
+        }
+        const long long kc = chunk_len(ksplit);
+        const size_t xbytes = static_cast<size_t>(rows) * (kc * 2 + kMmaRowPadBytes);
+        if (xbytes <= budget) {
+            const int grid = std::max(sm_count / ksplit, 1) * ksplit;
+            const long long groups = (pr.n + 7) / 8;
+            const long long kbc = kc / kStagedBlockK;
+            const long long total = groups * kbc;
+            long long active = std::min<long long>(static_cast<long long>(grid / ksplit) * warps, 2 * groups);
+            active = std::max<long long>(active, 1);
+            const long long span = (total + active - 1) / active;
+            active = (total + span - 1) / span;
+            plan->shape = kStagedShape;
+            plan->block = kStagedThreads;
+            plan->grid = static_cast<int>((active + warps - 1) / warps) * ksplit;
+            plan->ksplit = ksplit;
+            plan->active_warps = static_cast<int>(active);
+            plan->span = span;
+            plan->slots = static_cast<int>((kbc + span - 1) / span) + 1;
+            plan->smem_bytes = xbytes + staging;
+            plan->partial_floats = groups * ksplit * plan->slots * 128;
+            plan->counter_count = groups;
+            return true;
+        }
+    }
     if (shape < 0 || shape > 2) {
         // 16 activation rows: one 1024-thread CTA per SM leaves room for a longer K chunk (fewer partial sums)
         shape = (rows == 16) ? 1 : 0;
@@ -598,6 +862,14 @@ cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const Gem
             return launch_shape<KUDNN_B200_F16, true>(p, plan, plan.shape, unroll, stream);
         }
         return launch_shape<KUDNN_B200_BF16, true>(p, plan, plan.shape, unroll, stream);
+    }
+    if (plan.shape == kStagedShape) {
+        const long long kcs = ((pr.k + plan.ksplit - 1) / plan.ksplit + kStagedBlockK - 1) / kStagedBlockK * kStagedBlockK;
+        p.kc = static_cast<int>(kcs);
+        p.kb = static_cast<int>(kcs / kStagedBlockK);
+        p.total = ((pr.n + 7) / 8) * p.kb;
+        return dt == KUDNN_B200_F16 ? launch_mma_staged<KUDNN_B200_F16>(p, plan, stream)
+                                    : launch_mma_staged<KUDNN_B200_BF16>(p, plan, stream);
     }
     const long long kc = ((pr.k + plan.ksplit - 1) / plan.ksplit + 31) / 32 * 32;
     p.kc = static_cast<int>(kc);

@@ -46,6 +46,18 @@ cudaError_t launch_simt(const LinearProblem &pr, cudaStream_t stream);
 bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPlan *plan);
 cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const GemvWorkspace &ws, cudaStream_t stream);
 
+// Streaming kernel fed through a shared-memory ring (gemv_ring.cu): m <= 16, 16-bit types, k a multiple of 2048.
+struct RingPlan {
+    bool rows16;
+    int grid, ksplit, spg, kc, ctas_per_chunk;
+    long long range, total;
+    size_t smem_bytes;
+    long long partial_floats, counter_count;
+};
+bool gemv_ring_plan(const LinearProblem &pr, int sm_count, RingPlan *plan);
+cudaError_t launch_gemv_ring(const LinearProblem &pr, const RingPlan &plan, const GemvWorkspace &ws, DeviceStatus *status,
+                             cudaStream_t stream);
+
 // Tensor-core kernel.  Operands must be K-major with 16-byte aligned rows; see tc_eligible().
 struct TcOperands {
     const void *a;  // [m, k_total] K-major
@@ -59,6 +71,9 @@ struct TcPlan {
     int stages;
     int grid;
     size_t smem_bytes;
+    // split-K (splits > 1) for problems with far fewer tiles than SMs: the kernel is launched as clusters of
+    // `splits` CTAs, grid = tiles * splits
+    int splits, kb_per_split;
     unsigned char tmap_a[128] __attribute__((aligned(64)));
     unsigned char tmap_b[128] __attribute__((aligned(64)));
 };

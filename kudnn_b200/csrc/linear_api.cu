@@ -276,25 +276,71 @@ int pack_weights(Handle *h, const void *b_dev, DeviceBuffer *buf, bool with_raw,
         *ktotal = 3 * k_pad;
     } else {
         const long long k_pad = round_up(d.k, 8);
-        cudaError_t e = buf->reserve(static_cast<size_t>(d.n) * k_pad * 2);
+        const long long pitch = k_pad;
+        cudaError_t e = buf->reserve(static_cast<size_t>(d.n) * pitch * 2);
         if (e != cudaSuccess) {
             return fail_cuda(e, "packed weights");
         }
-        e = kb::launch_pack_kmajor(b_dev, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, buf->ptr, d.b_dtype, k_pad, k_pad, stream);
+        e = kb::launch_pack_kmajor(b_dev, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, buf->ptr, d.b_dtype, pitch, k_pad, stream);
         if (e != cudaSuccess) {
             return fail_cuda(e, "weight pack kernel");
         }
         *launches += 1;
-        *ld = k_pad;
+        *ld = pitch;
         *ktotal = d.k;
         *raw = buf->ptr;
     }
     return KUDNN_B200_OK;
 }
 
-// `d` is the handle's descriptor, or a copy of it restricted to a block of rows (host-pointer pipeline)
-int run_device(Handle *h, const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &args, cudaStream_t stream)
+// A batched problem whose weights are shared by all batch entries and whose other tensors are laid out so that
+// (batch index, row) is one linear row index is a 2-D problem with batch * m rows: [B, S, K] x [K, N], the way a
+// linear layer is applied to a batch of sequences.  Writes that 2-D descriptor and returns true when this holds.
+bool collapse_batch(const kudnn_b200_linear_desc &d, kudnn_b200_linear_desc *out)
 {
+    const long long e[3] = {batch_extent(d, 0), batch_extent(d, 1), batch_extent(d, 2)};
+    const long long nb = e[0] * e[1] * e[2];
+    if (nb == 1 || nb * d.m > 0x7fffffffll) {
+        return false;
+    }
+    for (int i = 0; i < 3; ++i) {
+        if (e[i] > 1 && d.b_sb[i] != 0) {
+            return false;
+        }
+    }
+    auto linear_rows = [&](const int64_t sb[3], long long s_m) {
+        long long expect = d.m * s_m;  // stride of the innermost batch dimension
+        for (int i = 2; i >= 0; --i) {
+            if (e[i] > 1 && sb[i] != expect) {
+                return false;
+            }
+            expect *= e[i];
+        }
+        return true;
+    };
+    if (!linear_rows(d.a_sb, d.a_sm) || !linear_rows(d.c_sb, d.c_sm)) {
+        return false;
+    }
+    if (d.has_bias != 0 && !linear_rows(d.bias_sb, d.bias_sm)) {
+        return false;
+    }
+    if (d.res_op != KUDNN_B200_RES_NONE && (!linear_rows(d.res_sb, d.res_sm) || !linear_rows(d.out_sb, d.out_sm))) {
+        return false;
+    }
+    *out = d;
+    out->m = nb * d.m;
+    for (int i = 0; i < 3; ++i) {
+        out->batch[i] = 1;
+        out->a_sb[i] = out->b_sb[i] = out->c_sb[i] = out->bias_sb[i] = out->res_sb[i] = out->out_sb[i] = 0;
+    }
+    return true;
+}
+
+// `d_in` is the handle's descriptor, or a copy of it restricted to a block of rows (host-pointer pipeline)
+int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_linear_args &args, cudaStream_t stream)
+{
+    kudnn_b200_linear_desc collapsed;
+    const kudnn_b200_linear_desc &d = collapse_batch(d_in, &collapsed) ? collapsed : d_in;
     if (args.a == nullptr || args.b == nullptr) {
         return fail(KUDNN_B200_BAD_ARGUMENTS, "run: a and b must not be null");
     }
@@ -330,34 +376,57 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d, const kudnn_b200_line
     }
 
     // ---- streaming kernels (m <= 16)
+    auto reserve_gemv_scratch = [&](long long partial_floats, long long counter_count, kb::GemvWorkspace *ws) -> int {
+        cudaError_t e = h->gemv_partials.reserve(static_cast<size_t>(partial_floats) * sizeof(float));
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "streaming-kernel scratch");
+        }
+        if (h->gemv_counters.bytes < static_cast<size_t>(counter_count) * sizeof(unsigned)) {
+            e = h->gemv_counters.reserve(static_cast<size_t>(counter_count) * sizeof(unsigned));
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "streaming-kernel counters");
+            }
+            e = cudaMemsetAsync(h->gemv_counters.ptr, 0, h->gemv_counters.bytes, stream);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "streaming-kernel counters");
+            }
+        }
+        ws->partials = static_cast<float *>(h->gemv_partials.ptr);
+        ws->counters = static_cast<unsigned *>(h->gemv_counters.ptr);
+        ws->partial_floats = static_cast<long long>(h->gemv_partials.bytes / sizeof(float));
+        ws->counter_count = static_cast<long long>(h->gemv_counters.bytes / sizeof(unsigned));
+        return KUDNN_B200_OK;
+    };
+    if (forced == KUDNN_B200_KERNEL_GEMV_RING) {
+        // Only on request: bulk copies into a shared-memory ring read HBM slower than plain 16-byte loads on this
+        // GPU (measured without any arithmetic), so the automatic choice never takes this kernel.
+        kb::RingPlan rplan;
+        if (two_d && d.m <= 16 && kb::gemv_ring_plan(pr, h->sm_count, &rplan)) {
+            kb::GemvWorkspace ws;
+            rc = reserve_gemv_scratch(rplan.partial_floats, rplan.counter_count, &ws);
+            if (rc != KUDNN_B200_OK) {
+                return rc;
+            }
+            cudaError_t e = kb::launch_gemv_ring(pr, rplan, ws, static_cast<kb::DeviceStatus *>(h->status.ptr), stream);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "ring streaming kernel launch");
+            }
+            h->last_kernel = KUDNN_B200_KERNEL_GEMV_RING;
+            h->last_launches = 1;
+            return KUDNN_B200_OK;
+        }
+        return fail(KUDNN_B200_UNSUPPORTED, "the ring streaming kernel needs m <= 16, 16-bit K-contiguous operands and k % 2048 == 0");
+    }
     if (two_d && d.m <= 16 &&
         (forced == KUDNN_B200_KERNEL_AUTO || forced == KUDNN_B200_KERNEL_GEMV_FMA || forced == KUDNN_B200_KERNEL_GEMV_MMA)) {
-        const kb::LinearProblem &gp = pr;
         kb::GemvPlan plan;
-        if (kb::gemv_plan(gp, h->sm_count, forced, &plan)) {
-            cudaError_t e = cudaSuccess;
-            if (h->gemv_partials.bytes < static_cast<size_t>(plan.partial_floats) * sizeof(float)) {
-                e = h->gemv_partials.reserve(static_cast<size_t>(plan.partial_floats) * sizeof(float));
-                if (e != cudaSuccess) {
-                    return fail_cuda(e, "streaming-kernel scratch");
-                }
-            }
-            if (h->gemv_counters.bytes < static_cast<size_t>(plan.counter_count) * sizeof(unsigned)) {
-                e = h->gemv_counters.reserve(static_cast<size_t>(plan.counter_count) * sizeof(unsigned));
-                if (e != cudaSuccess) {
-                    return fail_cuda(e, "streaming-kernel counters");
-                }
-                e = cudaMemsetAsync(h->gemv_counters.ptr, 0, h->gemv_counters.bytes, stream);
-                if (e != cudaSuccess) {
-                    return fail_cuda(e, "streaming-kernel counters");
-                }
-            }
+        if (kb::gemv_plan(pr, h->sm_count, forced, &plan)) {
             kb::GemvWorkspace ws;
-            ws.partials = static_cast<float *>(h->gemv_partials.ptr);
-            ws.counters = static_cast<unsigned *>(h->gemv_counters.ptr);
-            ws.partial_floats = static_cast<long long>(h->gemv_partials.bytes / sizeof(float));
-            ws.counter_count = static_cast<long long>(h->gemv_counters.bytes / sizeof(unsigned));
-            e = kb::launch_gemv(gp, plan, ws, stream);
+            rc = reserve_gemv_scratch(plan.partial_floats, plan.counter_count, &ws);
+            if (rc != KUDNN_B200_OK) {
+                return rc;
+            }
+            cudaError_t e = kb::launch_gemv(pr, plan, ws, stream);
             if (e != cudaSuccess) {
                 return fail_cuda(e, "streaming kernel launch");
             }
@@ -405,35 +474,37 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d, const kudnn_b200_line
             // activations
             if (f32) {
                 const long long k_pad = round_up(d.k, 32);
-                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * 3 * k_pad * sizeof(float));
+                const long long pitch = 3 * k_pad;
+                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * pitch * sizeof(float));
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "activation planes");
                 }
-                e = kb::launch_split_tf32(args.a, d.m, d.k, d.a_sm, d.a_sk, static_cast<float *>(h->a_scratch.ptr), 3 * k_pad,
+                e = kb::launch_split_tf32(args.a, d.m, d.k, d.a_sm, d.a_sk, static_cast<float *>(h->a_scratch.ptr), pitch,
                                           k_pad, 0, stream);
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "activation split kernel");
                 }
                 launches += 1;
                 ops.a = h->a_scratch.ptr;
-                ops.lda = 3 * k_pad;
+                ops.lda = pitch;
             } else if (kmajor_ready(args.a, d.a_dtype, d.a_sm, d.a_sk, d.m)) {
                 ops.a = args.a;
                 ops.lda = d.a_sm;
             } else {
                 const long long k_pad = round_up(d.k, 8);
-                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * k_pad * 2);
+                const long long pitch = k_pad;
+                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * pitch * 2);
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "packed activations");
                 }
-                e = kb::launch_pack_kmajor(args.a, d.a_dtype, d.m, d.k, d.a_sm, d.a_sk, h->a_scratch.ptr, d.a_dtype, k_pad,
+                e = kb::launch_pack_kmajor(args.a, d.a_dtype, d.m, d.k, d.a_sm, d.a_sk, h->a_scratch.ptr, d.a_dtype, pitch,
                                            k_pad, stream);
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "activation pack kernel");
                 }
                 launches += 1;
                 ops.a = h->a_scratch.ptr;
-                ops.lda = k_pad;
+                ops.lda = pitch;
             }
             if (!(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b && h->plan_m == d.m)) {
                 cudaError_t e = kb::tc_make_plan(ops, d.m, d.n, h->sm_count, &h->tc_plan);
@@ -716,6 +787,8 @@ int kudnn_b200_linear_create(const kudnn_b200_linear_desc *desc, kudnn_b200_line
             h->forced_kernel = KUDNN_B200_KERNEL_GEMV_FMA;
         } else if (std::strcmp(force, "gemv_mma") == 0) {
             h->forced_kernel = KUDNN_B200_KERNEL_GEMV_MMA;
+        } else if (std::strcmp(force, "gemv_ring") == 0) {
+            h->forced_kernel = KUDNN_B200_KERNEL_GEMV_RING;
         }
     }
     *handle = h;
@@ -991,7 +1064,7 @@ int kudnn_b200_linear_check(kudnn_b200_linear_t h, void *cuda_stream)
 
 int kudnn_b200_linear_force_kernel(kudnn_b200_linear_t h, int kernel)
 {
-    if (h == nullptr || kernel < KUDNN_B200_KERNEL_AUTO || kernel > KUDNN_B200_KERNEL_TC) {
+    if (h == nullptr || kernel < KUDNN_B200_KERNEL_AUTO || kernel > KUDNN_B200_KERNEL_GEMV_RING) {
         return fail(KUDNN_B200_BAD_ARGUMENTS, "force_kernel: bad argument");
     }
     h->forced_kernel = kernel;

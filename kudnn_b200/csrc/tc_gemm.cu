@@ -4,13 +4,13 @@
 // (src/dnn/src/matmul_jit/MatrixComputation/kudnn_default_impl_fp16fp16f32f32.cpp:900-983) and the BLAS calls of
 // src/dnn/src/kudnn_gemm.cpp:157-227.
 //
-// Shape of one CTA (320 threads, persistent over output tiles, one CTA per SM):
+// Shape of one CTA (448 threads, persistent over output tiles, one CTA per SM):
 //   warp 0      producer: one lane issues the TMA loads of the A tile [128 x 128 B] and the B tile [BN x 128 B]
 //               of every k-block into the ring (4 or 6 stages), 128-byte swizzle, completion on an mbarrier
 //   warp 1      one lane issues tcgen05.mma (M=128, N=BN, K=32 bytes per instruction, four per k-block) into one
 //               of two TMEM accumulators and commits to the stage's "empty" barrier / the tile's "full" barrier;
 //               the warp also owns TMEM allocation
-//   warps 2..9  epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; two warps share a lane quarter and
+//   warps 2..13 epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; three warps share a lane quarter and
 //               split the columns) 8 columns at a time, applies the post-GEMM chain and stores 16-byte vectors;
 //               the second accumulator lets this overlap the next tile's main loop
 // Operands are K-major ([rows, k], k contiguous).  16-bit inputs run as kind::f16 with fp32 accumulation.  fp32
@@ -24,16 +24,34 @@
 
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
+
+#ifdef KUDNN_B200_TC_TRACE
+__device__ long long g_tc_trace[160 * 16];
+#define TC_TRACE(slot)                                                                             \
+    do {                                                                                           \
+        long long t_;                                                                              \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                     \
+        g_tc_trace[blockIdx.x * 16 + (slot)] = t_;                                                 \
+    } while (0)
+extern "C" int kudnn_b200_debug_tc_trace(long long *out)
+{
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 160 * 16));
+}
+#else
+#define TC_TRACE(slot) do { } while (0)
+#endif
 
 namespace kb {
 
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kEpiWarps = 8;                       // two per scheduler: each hides the other's latencies
+constexpr int kEpiWarps = 12;                      // two per scheduler: each hides the other's latencies
 constexpr int kTcThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA, the rest: epilogue
 constexpr int kStageRowBytes = 128;  // one swizzle row: 64 16-bit or 32 32-bit elements
 constexpr int kABytes = kBM * kStageRowBytes;
@@ -47,6 +65,9 @@ struct TcParams {
     int tiles_m, tiles_n, num_tiles;
     unsigned idesc;
     DeviceStatus *status;
+    // split-K for problems with fewer tiles than SMs: the `splits` CTAs of a thread-block cluster share one tile,
+    // each contracts over kb_per_split k-blocks, and the partial tiles are added through distributed shared memory
+    int splits, kb_per_split;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -487,7 +508,13 @@ __device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const u
     float v[8], side[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-        v[j] = e.alpha * __uint_as_float(raw[j]);
+        v[j] = __uint_as_float(raw[j]);
+    }
+    if (e.alpha != 1.0f) {  // multiplying by exactly 1 changes nothing, so the common case skips the pass
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] *= e.alpha;
+        }
     }
     if (rp.bias_mode == 1) {
         load8_vec(rp.bias + byte_off_bias, e.bias_dtype, side);
@@ -579,14 +606,12 @@ __device__ __forceinline__ bool row_contiguous_aligned(const void *base, int dty
 // taddr.  The loop is rolled to keep the code small (a fully unrolled epilogue does not fit the instruction cache
 // and runs an order of magnitude slower); the TMEM load of the next group is in flight while the current one is
 // processed.  Rows whose tensors are contiguous and 16-byte aligned take the pointer-bumping fast path.
-template <int kAct, int kPrecise>
-__device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr, bool row_ok, long long mi, long long n0,
-                                             int groups)
+// Row-base pointers for the vector path of the epilogue.  Returns whether that path applies to the `groups` groups
+// of 8 columns starting at (mi, n0): whole groups inside n, no beta term, every tensor involved contiguous along n
+// and 16-byte aligned there.
+__device__ __forceinline__ bool setup_row_pointers(const EpiParams &e, bool row_ok, long long mi, long long n0, int groups,
+                                                   RowPointers &rp)
 {
-    if (groups <= 0) {
-        return;
-    }
-    RowPointers rp;
     rp.c = nullptr;
     rp.bias = nullptr;
     rp.res = nullptr;
@@ -620,6 +645,18 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
             rp.out = static_cast<char *>(e.out) + io * dtype_size(e.out_dtype);
         }
     }
+    return fast;
+}
+
+template <int kAct, int kPrecise>
+__device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr, bool row_ok, long long mi, long long n0,
+                                             int groups)
+{
+    if (groups <= 0) {
+        return;
+    }
+    RowPointers rp;
+    const bool fast = setup_row_pointers(e, row_ok, mi, n0, groups, rp);
     const int step_c = 8 * dtype_size(e.c_dtype), step_bias = 8 * dtype_size(e.bias_dtype);
     const int step_res = 8 * dtype_size(e.res_dtype), step_out = 8 * dtype_size(e.out_dtype);
 
@@ -644,10 +681,117 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
     }
 }
 
+// ---- split-K through a thread-block cluster
+// Every CTA of the cluster leaves its partial tile in its own shared memory as [128 rows][BN + 4 floats] (the four
+// extra floats put the 16-byte stores of 8 consecutive rows on distinct banks).  After a cluster barrier, CTA r adds,
+// for its 128 / splits rows, the partial tiles of all ranks in rank order (the result does not depend on timing) and
+// runs the post-GEMM chain for those rows.
+constexpr int kMaxSplits = 8;
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_smem_addr, uint32_t rank)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(remote)
+                 : "memory");
+    return v;
+}
+
+// Copies `groups` groups of 8 accumulator columns of this thread's row from TMEM to `dst` (shared memory).  The
+// loads are issued three groups at a time before the wait.
+__device__ __forceinline__ void dump_partial_row(uint32_t taddr, float *dst, int groups)
+{
+    for (int g0 = 0; g0 < groups; g0 += 3) {
+        uint32_t r[3][8];
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+            if (g0 + u < groups) {
+                tmem_load_8_issue(taddr + static_cast<uint32_t>((g0 + u) * 8), r[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+            if (g0 + u < groups) {
+                tmem_load_wait(r[u]);
+                float4 *out = reinterpret_cast<float4 *>(dst + (g0 + u) * 8);
+                out[0] = make_float4(__uint_as_float(r[u][0]), __uint_as_float(r[u][1]), __uint_as_float(r[u][2]),
+                                     __uint_as_float(r[u][3]));
+                out[1] = make_float4(__uint_as_float(r[u][4]), __uint_as_float(r[u][5]), __uint_as_float(r[u][6]),
+                                     __uint_as_float(r[u][7]));
+            }
+        }
+    }
+}
+
+// The epilogue threads of cluster rank `rank` finish rows [rank * 128 / splits, (rank + 1) * 128 / splits) of the tile.
+template <int kAct, int kPrecise, int kBN>
+__device__ __forceinline__ void finish_split_rows(const EpiParams &e, const float *part, int splits, uint32_t rank, int tm,
+                                                  int tn, int m, int n, int epi_tid)
+{
+    constexpr int kPitch = kBN + 4;
+    constexpr int kGroups = kBN / 8;
+    const int rows_per = kBM / splits;
+    const uint32_t part_addr = smem_u32(part);
+    for (int u = epi_tid; u < rows_per * kGroups; u += kEpiWarps * 32) {
+        const int r_local = u / kGroups, g = u - r_local * kGroups;
+        const int row = static_cast<int>(rank) * rows_per + r_local;
+        const long long mi = static_cast<long long>(tm) * kBM + row;
+        const long long ni = static_cast<long long>(tn) * kBN + g * 8;
+        if (mi >= m || ni >= n) {
+            continue;
+        }
+        const uint32_t addr = part_addr + static_cast<uint32_t>((row * kPitch + g * 8) * 4);
+        float4 lo[kMaxSplits], hi[kMaxSplits];
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) {
+            if (s < splits) {
+                lo[s] = ld_cluster_f4(addr, static_cast<uint32_t>(s));
+                hi[s] = ld_cluster_f4(addr + 16, static_cast<uint32_t>(s));
+            }
+        }
+        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) {
+            if (s < splits) {
+                acc[0] += lo[s].x; acc[1] += lo[s].y; acc[2] += lo[s].z; acc[3] += lo[s].w;
+                acc[4] += hi[s].x; acc[5] += hi[s].y; acc[6] += hi[s].z; acc[7] += hi[s].w;
+            }
+        }
+        uint32_t raw[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            raw[j] = __float_as_uint(acc[j]);
+        }
+        RowPointers rp;
+        if (setup_row_pointers(e, true, mi, ni, 1, rp)) {
+            epilogue_group8_fast<kAct, kPrecise>(e, raw, rp, 0, 0, 0, 0);
+        } else {
+            epilogue_group8<kAct, kPrecise>(e, raw, mi, ni);
+        }
+    }
+}
+
 template <int kKind, int kBN>
 __global__ void __launch_bounds__(kTcThreads, 1)
     tc_linear_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     const TcParams p)
+                     const __grid_constant__ TcParams p)
 {
     constexpr int kBBytes = kBN * kStageRowBytes;
     constexpr int kStageBytes = kABytes + kBBytes;
@@ -689,10 +833,16 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (threadIdx.x == 0) {
+        TC_TRACE(0);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {
+        TC_TRACE(1);
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
@@ -702,7 +852,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             int stage = 0;
             uint32_t phase = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
+            for (int item = blockIdx.x; alive && item < p.num_tiles * p.splits; item += gridDim.x) {
+                const int tile = item / p.splits, split = item - tile * p.splits;
+                const int kb_begin = split * p.kb_per_split;
+                const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
                 const int per_group = kGroupM * p.tiles_n;
                 const int group = tile / per_group;
                 const int first_m = group * kGroupM;
@@ -710,7 +863,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 const int in_group = tile - group * per_group;
                 const int tm = first_m + in_group % gsize;
                 const int tn = in_group / gsize;
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag, p.status, 1)) {
                         alive = false;
                         break;
@@ -726,6 +879,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                     }
                 }
             }
+            TC_TRACE(2);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -735,13 +889,16 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             int acc = 0;
             uint32_t acc_phase = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
+            for (int item = blockIdx.x; alive && item < p.num_tiles * p.splits; item += gridDim.x) {
+                const int split = item % p.splits;
+                const int kb_begin = split * p.kb_per_split;
+                const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
                 if (!mbar_wait(tmem_empty + acc, acc_phase ^ 1u, abort_flag, p.status, 2)) {
                     break;
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBN);
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(full_bar + stage, phase, abort_flag, p.status, 3)) {
                         alive = false;
                         break;
@@ -754,7 +911,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                     for (int ks = 0; ks < 4; ++ks) {
                         // 32 bytes along k inside the swizzle row = 2 units of the 16-byte address field
                         umma<kKind>(tmem_d, adesc + static_cast<uint64_t>(2 * ks), bdesc + static_cast<uint64_t>(2 * ks),
-                                    p.idesc, (kb | ks) != 0 ? 1u : 0u);
+                                    p.idesc, (kb != kb_begin || ks != 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar + stage);
                     if (++stage == kStages) {
@@ -766,6 +923,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                     break;
                 }
                 umma_commit(tmem_full + acc);
+                TC_TRACE(3);
                 acc ^= 1;
                 if (acc == 0) {
                     acc_phase ^= 1u;
@@ -780,7 +938,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const EpiParams &e = p.epi;
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < p.num_tiles * p.splits; item += gridDim.x) {
+            const int tile = item / p.splits;
             const int per_group = kGroupM * p.tiles_n;
             const int group = tile / per_group;
             const int first_m = group * kGroupM;
@@ -788,7 +947,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const int in_group = tile - group * per_group;
             const int tm = first_m + in_group % gsize;
             const int tn = in_group / gsize;
-            if (!mbar_wait(tmem_full + acc, acc_phase, abort_flag, p.status, 4)) {
+            const bool arrived = mbar_wait(tmem_full + acc, acc_phase, abort_flag, p.status, 4);
+            if (threadIdx.x == 64) {
+                TC_TRACE(4);
+            }
+            if (!arrived && p.splits == 1) {
                 break;
             }
             tc_fence_after();
@@ -796,13 +959,34 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const bool row_ok = mi < p.m;
             const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                        static_cast<uint32_t>(acc * kBN);
-            constexpr int kPartCols = kBN / (kEpiWarps / 4);
-            const long long n0 = static_cast<long long>(tn) * kBN + part * kPartCols;
+            // the warps that share a lane quarter split the tile's 8-column groups between them
+            constexpr int kParts = kEpiWarps / 4, kGroups = kBN / 8;
+            const int g_begin = part * kGroups / kParts, g_end = (part + 1) * kGroups / kParts;
+            const long long n0 = static_cast<long long>(tn) * kBN + g_begin * 8;
             long long cols = p.n - n0;
-            cols = cols < 0 ? 0 : (cols < kPartCols ? cols : kPartCols);
+            const long long part_cols = static_cast<long long>(g_end - g_begin) * 8;
+            cols = cols < 0 ? 0 : (cols < part_cols ? cols : part_cols);
             const int groups = static_cast<int>((cols + 7) / 8);
-            const uint32_t taddr_part = taddr_row + static_cast<uint32_t>(part * kPartCols);
+            const uint32_t taddr_part = taddr_row + static_cast<uint32_t>(g_begin * 8);
             const bool precise = e.c_dtype == KUDNN_B200_F32;
+            if (p.splits > 1) {
+                // partial tile -> this CTA's shared memory (the stage buffers: every load into them has landed and
+                // every MMA that read them has completed once the accumulator barrier has fired); it is added to
+                // the other ranks' tiles after the role branches, where all warps of the cluster meet
+                if (arrived) {
+                    float *part = reinterpret_cast<float *>(smem);
+                    dump_partial_row(taddr_part, part + row_in_tile * (kBN + 4) + g_begin * 8, g_end - g_begin);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(tmem_empty + acc);
+                    }
+                }
+                if (threadIdx.x == 64) {
+                    TC_TRACE(5);
+                }
+                break;  // one work item per CTA in this mode
+            }
             switch (e.act) {
                 case KUDNN_B200_ACT_NONE:
                     epilogue_row<KUDNN_B200_ACT_NONE, 0>(e, taddr_part, row_ok, mi, n0, groups);
@@ -833,11 +1017,71 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             if (lane == 0) {
                 mbar_arrive(tmem_empty + acc);
             }
+            if (threadIdx.x == 64) {
+                TC_TRACE(10);
+            }
             acc ^= 1;
             if (acc == 0) {
                 acc_phase ^= 1u;
             }
         }
+    }
+    if (threadIdx.x == 0) {
+        TC_TRACE(11);
+    }
+
+    if (p.splits > 1) {
+        // ------------------------------------------------------------------ split-K: add the cluster's partial tiles
+        __syncwarp();
+        cluster_sync_all();  // all partial tiles are in place (a hardware barrier over every thread of the cluster)
+        if (threadIdx.x == 64) {
+            TC_TRACE(6);
+        }
+        if (warp >= 2 && *abort_flag == 0) {
+            const int tile = static_cast<int>(blockIdx.x) / p.splits;
+            const int per_group = kGroupM * p.tiles_n;
+            const int group = tile / per_group;
+            const int first_m = group * kGroupM;
+            const int gsize = (p.tiles_m - first_m < kGroupM) ? (p.tiles_m - first_m) : kGroupM;
+            const int in_group = tile - group * per_group;
+            const int tm = first_m + in_group % gsize;
+            const int tn = in_group / gsize;
+            const float *part = reinterpret_cast<const float *>(smem);
+            const EpiParams &e = p.epi;
+            const uint32_t rank = cluster_rank();
+            const int epi_tid = static_cast<int>(threadIdx.x) - 64;
+            const bool precise = e.c_dtype == KUDNN_B200_F32;
+            switch (e.act) {
+                case KUDNN_B200_ACT_NONE:
+                    finish_split_rows<KUDNN_B200_ACT_NONE, 0, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    break;
+                case KUDNN_B200_ACT_RELU:
+                    finish_split_rows<KUDNN_B200_ACT_RELU, 0, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    break;
+                case KUDNN_B200_ACT_SWISH:
+                    if (precise) {
+                        finish_split_rows<KUDNN_B200_ACT_SWISH, 1, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    } else {
+                        finish_split_rows<KUDNN_B200_ACT_SWISH, 0, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    }
+                    break;
+                case KUDNN_B200_ACT_GELU_TANH:
+                    if (precise) {
+                        finish_split_rows<KUDNN_B200_ACT_GELU_TANH, 1, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    } else {
+                        finish_split_rows<KUDNN_B200_ACT_GELU_TANH, 0, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    }
+                    break;
+                default:
+                    finish_split_rows<-1, -1, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    break;
+            }
+        }
+        if (threadIdx.x == 64) {
+            TC_TRACE(7);
+        }
+        __syncwarp();
+        cluster_sync_all();  // no CTA leaves while another still reads its shared memory
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -855,6 +1099,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     }
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (threadIdx.x == 0) {
+        TC_TRACE(12);
     }
 }
 
@@ -923,6 +1170,22 @@ cudaError_t launch_one(const TcPlan &plan, const TcParams &p, cudaStream_t strea
     CUtensorMap ta, tb;
     std::memcpy(&ta, plan.tmap_a, sizeof(ta));
     std::memcpy(&tb, plan.tmap_b, sizeof(tb));
+    if (plan.splits > 1) {
+        // the CTAs that share a tile form a cluster; blockIdx.x = tile * splits + rank
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(plan.grid), 1, 1);
+        cfg.blockDim = dim3(kTcThreads, 1, 1);
+        cfg.dynamicSmemBytes = plan.smem_bytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = static_cast<unsigned>(plan.splits);
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+    }
     kernel<<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(ta, tb, p);
     return cudaGetLastError();
 }
@@ -955,7 +1218,31 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     }
     plan->block_n = bn;
     plan->stages = (bn == 256) ? 4 : 6;
-    plan->grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+    // Split-K: with at most half the SMs busy and a long K, the CTAs of a cluster share a tile and cut K between
+    // them (2, 4 or 8 ways: the rows of the tile are divided among the ranks for the final pass).  Each split keeps
+    // at least four k-blocks so that the pipeline still fills, and no split may be empty.
+    const int elems_per_row = kStageRowBytes / dtype_size(ops.kind);
+    const long long num_kb = (ops.k_total + elems_per_row - 1) / elems_per_row;
+    long long splits = 1;
+    if (tiles * 2 <= sm_count && num_kb >= 8) {
+        long long want = std::min<long long>(sm_count / tiles, num_kb / 4);
+        if (const char *env = std::getenv("KUDNN_B200_TC_SPLITS")) {
+            const long long v = std::atoll(env);
+            if (v >= 1 && v <= num_kb) {
+                want = v;
+            }
+        }
+        while (splits * 2 <= want && splits * 2 <= kMaxSplits) {
+            splits *= 2;
+        }
+        while (splits > 1 && (num_kb + (num_kb + splits - 1) / splits - 1) / ((num_kb + splits - 1) / splits) != splits) {
+            splits /= 2;
+        }
+    }
+    plan->splits = static_cast<int>(splits);
+    plan->kb_per_split = static_cast<int>((num_kb + splits - 1) / splits);
+    const long long items = tiles * splits;
+    plan->grid = splits > 1 ? static_cast<int>(items) : static_cast<int>(tiles < sm_count ? tiles : sm_count);
     plan->smem_bytes = static_cast<size_t>(plan->stages) * (kABytes + bn * kStageRowBytes) + 1024 + 256;
     CUtensorMap ta, tb;
     cudaError_t e = encode_kmajor(&ta, ops.a, ops.kind, m, ops.k_total, ops.lda, kBM);
@@ -985,6 +1272,8 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.num_tiles = p.tiles_m * p.tiles_n;
     p.idesc = make_idesc(ops.kind, plan.block_n);
     p.status = status;
+    p.splits = plan.splits;
+    p.kb_per_split = plan.kb_per_split;
     if (plan.block_n == 256) {
         switch (ops.kind) {
             case KUDNN_B200_F32:

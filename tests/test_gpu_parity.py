@@ -58,6 +58,18 @@ def test_simt_batched_with_broadcast(cuda_device, dtype, batch, a_bcast, b_bcast
     helpers.parity(case, cuda_device, acc=ko.ACC_F64, expect_kernel=kb.KERNEL_SIMT)
 
 
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("batch,m,expect", [((2, 3), 100, kb.KERNEL_TC), ((4,), 130, kb.KERNEL_TC),
+                                            ((2, 2), 1, "streaming")])
+def test_batched_shared_weights_run_as_rows(cuda_device, dtype, batch, m, expect):
+    """[B, S, K] x [K, N] with contiguous batches is one 2-D problem of B*S rows and takes the fast kernels."""
+    case = dict(m=m, n=264, k=512, dtype=dtype, bias="row", act=kb.ACT_SWISH, res_op=kb.RES_IDENTICAL, batch=batch,
+                b_bcast=True, x_dist="normal", w_std=0.03, seed=25)
+    info = helpers.parity(case, cuda_device, acc=ko.ACC_F64, expect_kernel=None if expect == "streaming" else expect)
+    if expect == "streaming":  # four rows: one of the streaming kernels, whichever the dispatcher prefers
+        assert info["kernel"] in [kb.KERNEL_NAMES[i] for i in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA, kb.KERNEL_GEMV_RING)]
+
+
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
 def test_alpha_beta(cuda_device, dtype):
     case = dict(m=50, n=70, k=64, dtype=dtype, bias="row", alpha=0.5, beta=0.25, seed=25)
@@ -73,19 +85,51 @@ def test_gemv_fma(cuda_device, dtype, m):
     helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_FMA, expect_kernel=kb.KERNEL_GEMV_FMA)
 
 
+@pytest.mark.parametrize("staged", ["1", "0"])
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 @pytest.mark.parametrize("m", [1, 3, 4, 7, 8, 9, 16])
-def test_gemv_mma(cuda_device, dtype, m):
+def test_gemv_mma(cuda_device, monkeypatch, staged, dtype, m):
+    monkeypatch.setenv("KUDNN_B200_GEMV_STAGED", staged)  # weight feed: through per-warp staging, or fragment-shaped loads
     case = dict(m=m, n=1003, k=1048, dtype=dtype, res_op=kb.RES_ELTWISE_MUL, x_dist="normal", w_std=0.05, seed=32)
     helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_MMA, expect_kernel=kb.KERNEL_GEMV_MMA)
 
 
+@pytest.mark.parametrize("staged", ["1", "0"])
 @pytest.mark.parametrize("kernel", [kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA])
-@pytest.mark.parametrize("n,k", [(8, 8), (5, 4096), (40000, 64), (777, 2504)])
-def test_gemv_shapes_that_cut_units(cuda_device, kernel, n, k):
+@pytest.mark.parametrize("n,k", [(8, 8), (5, 4096), (40000, 64), (777, 2504), (2600, 16384), (300, 8192)])
+def test_gemv_shapes_that_cut_units(cuda_device, monkeypatch, staged, kernel, n, k):
+    monkeypatch.setenv("KUDNN_B200_GEMV_STAGED", staged)
     # tiny, one long row, many short rows, odd sizes: exercise whole units, split units and idle warps
     case = dict(m=2, n=n, k=k, dtype="bf16", bias="row", x_dist="normal", w_std=0.05, seed=33)
     helpers.parity(case, cuda_device, kernel=kernel, expect_kernel=kernel)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m", [1, 4, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(1003, 2048), (520, 4096), (300, 8192), (8, 2048), (2600, 16384)])
+def test_gemv_ring(cuda_device, dtype, m, n, k):
+    case = dict(m=m, n=n, k=k, dtype=dtype, bias="row", act=kb.ACT_SWISH, res_op=kb.RES_ELTWISE_MUL, x_dist="normal",
+                w_std=0.02, seed=35)
+    helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_RING, expect_kernel=kb.KERNEL_GEMV_RING)
+
+
+@pytest.mark.parametrize("m", [4, 16])
+def test_decode_default_is_deterministic(cuda_device, m):
+    case = dict(m=m, n=4096, k=4096, dtype="bf16", res_op=kb.RES_ELTWISE_MUL, x_dist="normal", w_std=0.02, seed=36)
+    desc, arrays, c = helpers.build_case(case)
+    d = {k: helpers._to_torch(v, cuda_device) for k, v in arrays.items()}
+    lin = kb.Linear(desc)
+    outs = []
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        t_o = torch.zeros((1, m, 4096), dtype=torch.int16, device=cuda_device)
+        lin.run(d["a"], d["b"], None, None, d["res"], t_o, stream=stream)
+        lin.check(stream=stream)
+        outs.append(helpers._from_torch(t_o))
+    assert lin.last_kernel == kb.KERNEL_GEMV_MMA
+    _, ref_o = helpers.run_oracle(desc, arrays, c)
+    helpers.compare(outs[0], ref_o, desc.out_dtype)
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
 
 
 def test_gemv_repeated_calls_leave_counters_clean(cuda_device):
@@ -101,7 +145,7 @@ def test_gemv_repeated_calls_leave_counters_clean(cuda_device):
         lin.run(d["a"], d["b"], t_c, None, d["res"], t_o, stream=torch.cuda.current_stream().cuda_stream)
         lin.check(stream=torch.cuda.current_stream().cuda_stream)
         outs.append(helpers._from_torch(t_o))
-    assert lin.last_kernel == kb.KERNEL_GEMV_MMA
+    assert lin.last_kernel in (kb.KERNEL_GEMV_MMA, kb.KERNEL_GEMV_RING)
     helpers.compare(outs[0], ref_o, desc.out_dtype)
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])  # slot-ordered sums: deterministic
 
@@ -148,6 +192,25 @@ def test_tc_unaligned_n_and_only_second_output(cuda_device):
 def test_tc_alpha_beta(cuda_device):
     case = dict(m=256, n=256, k=256, dtype="bf16", bias="row", alpha=0.5, beta=0.25, w_std=0.05, seed=46)
     helpers.parity(case, cuda_device, kernel=kb.KERNEL_TC, expect_kernel=kb.KERNEL_TC)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("splits", [None, "1", "3", "64"])
+@pytest.mark.parametrize("m,n,k", [(128, 1024, 1024), (100, 200, 2056), (300, 130, 1000)])
+def test_tc_split_k(cuda_device, monkeypatch, dtype, splits, m, n, k):
+    """Few tiles and a long K: K is cut over several CTAs, partial tiles meet in scratch, the last arriver finishes.
+    The result must not depend on the cut beyond fp32 summation order, and repeated calls must agree bit for bit."""
+    if splits is not None:
+        monkeypatch.setenv("KUDNN_B200_TC_SPLITS", splits)
+    case = dict(m=m, n=n, k=k, dtype=dtype, bias="row", act=kb.ACT_SWISH, res_op=kb.RES_EXT, gamma=0.5, x_dist="normal",
+                w_std=0.02, seed=48)
+    desc, arrays, c = helpers.build_case(case)
+    ref_c, ref_o = helpers.run_oracle(desc, arrays, c, acc=ko.ACC_F64)
+    first = helpers.run_gpu(desc, arrays, c, cuda_device, kernel=kb.KERNEL_TC)
+    second = helpers.run_gpu(desc, arrays, c, cuda_device, kernel=kb.KERNEL_TC)
+    helpers.compare(first[0], ref_c, desc.c_dtype)
+    helpers.compare(first[1], ref_o, desc.out_dtype)
+    assert np.array_equal(first[0], second[0]) and np.array_equal(first[1], second[1])
 
 
 def test_tc_agrees_with_general_kernel(cuda_device):
@@ -292,7 +355,7 @@ def test_config4_decode_gate_full(cuda_device, m):
     lin = kb.Linear(desc)
     lin.run(x, w, None, None, gate, out, stream=torch.cuda.current_stream().cuda_stream)
     lin.check(stream=torch.cuda.current_stream().cuda_stream)
-    assert lin.last_kernel in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA)
+    assert lin.last_kernel in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA, kb.KERNEL_GEMV_RING)
     info = _check_rows(desc, x, w, None, gate, None, out, list(range(m)))
     assert info["out"]["bit_exact_fraction"] > 0.98
 

@@ -74,6 +74,7 @@ struct TcPlan {
     // split-K (splits > 1) for problems with far fewer tiles than SMs: the kernel is launched as clusters of
     // `splits` CTAs, grid = tiles * splits
     int splits, kb_per_split;
+    int pair;      // 1: clusters of two CTAs share 256 x block_n tiles (cta_group::2)
     unsigned char tmap_a[128] __attribute__((aligned(64)));
     unsigned char tmap_b[128] __attribute__((aligned(64)));
 };

@@ -515,6 +515,15 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
                 h->plan_b = ops.b;
                 h->plan_m = d.m;
                 h->plan_valid = true;
+                if (const char *dbg = std::getenv("KUDNN_B200_DEBUG")) {
+                    if (*dbg != '\0' && *dbg != '0') {
+                        std::fprintf(stderr, "kudnn_b200: tensor-core plan m=%lld n=%lld k=%lld: tile %s x %d, %d stages, grid %d, "
+                                             "k splits %d, %zu bytes of shared memory\n",
+                                     static_cast<long long>(d.m), static_cast<long long>(d.n), static_cast<long long>(d.k),
+                                     h->tc_plan.pair ? "256 (CTA pair)" : "128", h->tc_plan.block_n, h->tc_plan.stages,
+                                     h->tc_plan.grid, h->tc_plan.splits, h->tc_plan.smem_bytes);
+                    }
+                }
             }
             cudaError_t e = kb::launch_tc(ops, h->tc_plan, pr.epi, d.m, d.n,
                                           static_cast<kb::DeviceStatus *>(h->status.ptr), stream);

@@ -57,6 +57,8 @@ constexpr int kStageRowBytes = 128;  // one swizzle row: 64 16-bit or 32 32-bit 
 constexpr int kABytes = kBM * kStageRowBytes;
 constexpr int kGroupM = 16;  // tile rows per raster group
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about two seconds at 2 GHz
+constexpr int kWarpBiasFloats = 96;  // per epilogue warp: the bias values of its columns of the current tile, as fp32
+constexpr int kTailBytes = 256 + kEpiWarps * kWarpBiasFloats * 4;  // barriers and flags, then the bias slices
 
 struct TcParams {
     EpiParams epi;
@@ -145,6 +147,33 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *t
         : "memory");
 }
 
+// ---- CTA pair (cluster of two, tcgen05 cta_group::2) -----------------------------------------------------------
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_smem_addr, uint32_t rank)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+    return remote;
+}
+
+// Tile load of one CTA of a pair: the data lands in this CTA's shared memory, the bytes are counted on the leader's
+// barrier (a cluster address).  No data is shared between CTAs by this copy.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *tmap, uint32_t leader_bar_addr, int x,
+                                                 int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+        "[%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(tmap), "r"(leader_bar_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Arrival on a barrier of another CTA of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before()
 {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -189,6 +218,42 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
             "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
             : "memory");
     }
+}
+
+// One MMA over both CTAs of a pair: M = 256 (128 rows of A and of the accumulator per CTA), B = N / 2 rows from
+// each CTA's shared memory at the same offsets.  Issued by one thread of the leader CTA.
+template <int kKind>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    if (kKind == KUDNN_B200_F32) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+            "}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// Completion of all MMAs issued so far by this thread, signalled on the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar)
+{
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"(static_cast<unsigned short>(3))
+        : "memory");
 }
 
 __device__ __forceinline__ void umma_commit(uint64_t *bar)
@@ -429,7 +494,8 @@ struct RowPointers {
     const char *res;
     char *out;
     float bias_scalar;  // bias that does not vary along the row (column vector or single value)
-    int bias_mode;      // 0 none, 1 per-column values read from `bias`, 2 bias_scalar
+    int bias_mode;      // 0 none, 1 per-column values read from `bias`, 2 bias_scalar, 3 fp32 values in bias_smem
+    const float *bias_smem;  // the warp's slice of pre-loaded bias values, 8 per column group
 };
 
 __device__ __forceinline__ void load8_vec(const char *p, int dtype, float (&o)[8])
@@ -502,7 +568,8 @@ __device__ __forceinline__ void round_rne8(float (&v)[8])
 // all 8 columns in range.  Same arithmetic, no address arithmetic beyond pointer bumps.
 template <int kAct, int kPrecise>
 __device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const uint32_t (&raw)[8], const RowPointers &rp,
-                                                     int byte_off_c, int byte_off_bias, int byte_off_res, int byte_off_out)
+                                                     int byte_off_c, int byte_off_bias, int byte_off_res, int byte_off_out,
+                                                     int g)
 {
     const int ct = e.c_dtype;
     float v[8], side[8];
@@ -516,7 +583,12 @@ __device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const u
             v[j] *= e.alpha;
         }
     }
-    if (rp.bias_mode == 1) {
+    if (rp.bias_mode == 3) {
+        const float4 b0 = *reinterpret_cast<const float4 *>(rp.bias_smem + g * 8);
+        const float4 b1 = *reinterpret_cast<const float4 *>(rp.bias_smem + g * 8 + 4);
+        side[0] = b0.x; side[1] = b0.y; side[2] = b0.z; side[3] = b0.w;
+        side[4] = b1.x; side[5] = b1.y; side[6] = b1.z; side[7] = b1.w;
+    } else if (rp.bias_mode == 1) {
         load8_vec(rp.bias + byte_off_bias, e.bias_dtype, side);
     } else {
 #pragma unroll
@@ -618,6 +690,7 @@ __device__ __forceinline__ bool setup_row_pointers(const EpiParams &e, bool row_
     rp.out = nullptr;
     rp.bias_scalar = 0.0f;
     rp.bias_mode = 0;
+    rp.bias_smem = nullptr;
     bool fast = row_ok && e.beta == 0.0f && (n0 + static_cast<long long>(groups) * 8 <= e.n);
     if (fast) {
         if (e.c != nullptr) {
@@ -650,13 +723,17 @@ __device__ __forceinline__ bool setup_row_pointers(const EpiParams &e, bool row_
 
 template <int kAct, int kPrecise>
 __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr, bool row_ok, long long mi, long long n0,
-                                             int groups)
+                                             int groups, const float *staged_bias)
 {
     if (groups <= 0) {
         return;
     }
     RowPointers rp;
     const bool fast = setup_row_pointers(e, row_ok, mi, n0, groups, rp);
+    if (staged_bias != nullptr && rp.bias_mode == 1) {
+        rp.bias_mode = 3;
+        rp.bias_smem = staged_bias;
+    }
     const int step_c = 8 * dtype_size(e.c_dtype), step_bias = 8 * dtype_size(e.bias_dtype);
     const int step_res = 8 * dtype_size(e.res_dtype), step_out = 8 * dtype_size(e.out_dtype);
 
@@ -674,7 +751,7 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
             tmem_load_8_issue(taddr + static_cast<uint32_t>((g + 1) * 8), next);
         }
         if (fast) {
-            epilogue_group8_fast<kAct, kPrecise>(e, cur, rp, g * step_c, g * step_bias, g * step_res, g * step_out);
+            epilogue_group8_fast<kAct, kPrecise>(e, cur, rp, g * step_c, g * step_bias, g * step_res, g * step_out, g);
         } else if (row_ok) {
             epilogue_group8<kAct, kPrecise>(e, cur, mi, n0 + g * 8);
         }
@@ -781,21 +858,26 @@ __device__ __forceinline__ void finish_split_rows(const EpiParams &e, const floa
         }
         RowPointers rp;
         if (setup_row_pointers(e, true, mi, ni, 1, rp)) {
-            epilogue_group8_fast<kAct, kPrecise>(e, raw, rp, 0, 0, 0, 0);
+            epilogue_group8_fast<kAct, kPrecise>(e, raw, rp, 0, 0, 0, 0, 0);
         } else {
             epilogue_group8<kAct, kPrecise>(e, raw, mi, ni);
         }
     }
 }
 
-template <int kKind, int kBN>
+// kPair: two CTAs (a cluster of two SMs) work on a 256 x kBN tile with cta_group::2 MMAs.  Each CTA loads its 128
+// rows of A and half of the B rows, so a k-block costs an SM 32 KiB of L2 traffic instead of the 48 KiB of the
+// single-CTA 128 x 256 tile; the single-CTA kernel is limited by exactly that traffic.  Rank 0 of the pair (the
+// leader) owns the "full" barriers, issues all MMAs and releases the stages of both CTAs.
+template <int kKind, int kBN, bool kPair>
 __global__ void __launch_bounds__(kTcThreads, 1)
     tc_linear_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ TcParams p)
 {
-    constexpr int kBBytes = kBN * kStageRowBytes;
+    constexpr int kBRows = kPair ? kBN / 2 : kBN;  // rows of B this CTA loads per k-block
+    constexpr int kBBytes = kBRows * kStageRowBytes;
     constexpr int kStageBytes = kABytes + kBBytes;
-    constexpr int kStages = (kBN == 256) ? 4 : 6;
+    constexpr int kStages = (kBRows == 256) ? 4 : 6;
     constexpr int kTmemCols = 2 * kBN;
     constexpr int kElemsPerRow = (kKind == KUDNN_B200_F32) ? 32 : 64;  // elements per 128-byte k-block row
 
@@ -821,28 +903,43 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tmem_full + a, 1);
-            mbar_init(tmem_empty + a, kEpiWarps);
+            mbar_init(tmem_empty + a, kPair ? 2 * kEpiWarps : kEpiWarps);  // pair: the epilogue warps of both CTAs
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"(kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (kPair) {
+            // executed by the same warp of both CTAs with the same destination offset
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"(kTmemCols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"(kTmemCols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     if (threadIdx.x == 0) {
         TC_TRACE(0);
     }
     tc_fence_before();
     __syncthreads();
+    if (kPair) {
+        cluster_sync_all();  // the peer's barriers are initialised before anything is signalled on them
+    }
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) {
         TC_TRACE(1);
     }
+    // work items: tiles (x splits) over CTAs, or pair tiles over clusters of two
+    const uint32_t pair_rank = kPair ? cluster_rank() : 0u;
+    const int first_item = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int item_stride = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
@@ -852,7 +949,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             int stage = 0;
             uint32_t phase = 0;
             bool alive = true;
-            for (int item = blockIdx.x; alive && item < p.num_tiles * p.splits; item += gridDim.x) {
+            for (int item = first_item; alive && item < p.num_tiles * p.splits; item += item_stride) {
                 const int tile = item / p.splits, split = item - tile * p.splits;
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
@@ -861,8 +958,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 const int first_m = group * kGroupM;
                 const int gsize = (p.tiles_m - first_m < kGroupM) ? (p.tiles_m - first_m) : kGroupM;
                 const int in_group = tile - group * per_group;
-                const int tm = first_m + in_group % gsize;
                 const int tn = in_group / gsize;
+                // row of 128-row blocks this CTA loads: the pair's tile is 256 rows tall
+                const int tm = kPair ? 2 * (first_m + in_group % gsize) + static_cast<int>(pair_rank)
+                                     : first_m + in_group % gsize;
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag, p.status, 1)) {
                         alive = false;
@@ -870,9 +969,20 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                     }
                     unsigned char *sa = smem + stage * kStageBytes;
                     unsigned char *sb = sa + kABytes;
-                    mbar_expect_tx(full_bar + stage, kStageBytes);
-                    tma_load_2d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM);
-                    tma_load_2d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN);
+                    if (kPair) {
+                        // both CTAs' bytes are counted on the leader's barrier; only the leader announces them
+                        if (pair_rank == 0) {
+                            mbar_expect_tx(full_bar + stage, 2 * kStageBytes);
+                        }
+                        const uint32_t leader_bar = map_to_rank(smem_u32(full_bar + stage), 0u);
+                        tma_load_2d_pair(sa, &tmap_a, leader_bar, kb * kElemsPerRow, tm * kBM);
+                        tma_load_2d_pair(sb, &tmap_b, leader_bar, kb * kElemsPerRow,
+                                         tn * kBN + static_cast<int>(pair_rank) * kBRows);
+                    } else {
+                        mbar_expect_tx(full_bar + stage, kStageBytes);
+                        tma_load_2d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM);
+                        tma_load_2d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN);
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -883,13 +993,13 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && pair_rank == 0) {  // in a pair, the leader issues for both CTAs
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool alive = true;
-            for (int item = blockIdx.x; alive && item < p.num_tiles * p.splits; item += gridDim.x) {
+            for (int item = first_item; alive && item < p.num_tiles * p.splits; item += item_stride) {
                 const int split = item % p.splits;
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
@@ -910,10 +1020,20 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
                         // 32 bytes along k inside the swizzle row = 2 units of the 16-byte address field
-                        umma<kKind>(tmem_d, adesc + static_cast<uint64_t>(2 * ks), bdesc + static_cast<uint64_t>(2 * ks),
-                                    p.idesc, (kb != kb_begin || ks != 0) ? 1u : 0u);
+                        if (kPair) {
+                            umma_pair<kKind>(tmem_d, adesc + static_cast<uint64_t>(2 * ks),
+                                             bdesc + static_cast<uint64_t>(2 * ks), p.idesc,
+                                             (kb != kb_begin || ks != 0) ? 1u : 0u);
+                        } else {
+                            umma<kKind>(tmem_d, adesc + static_cast<uint64_t>(2 * ks), bdesc + static_cast<uint64_t>(2 * ks),
+                                        p.idesc, (kb != kb_begin || ks != 0) ? 1u : 0u);
+                        }
                     }
-                    umma_commit(empty_bar + stage);
+                    if (kPair) {
+                        umma_commit_pair(empty_bar + stage);  // frees the stage in both CTAs
+                    } else {
+                        umma_commit(empty_bar + stage);
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -922,7 +1042,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 if (!alive) {
                     break;
                 }
-                umma_commit(tmem_full + acc);
+                if (kPair) {
+                    umma_commit_pair(tmem_full + acc);  // both CTAs' epilogue warps wait on their own copy
+                } else {
+                    umma_commit(tmem_full + acc);
+                }
                 TC_TRACE(3);
                 acc ^= 1;
                 if (acc == 0) {
@@ -936,17 +1060,40 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const int row_in_tile = quarter * 32 + lane;
         const int part = (warp - 2) / 4;  // warps sharing a quarter split the tile's columns between them
         const EpiParams &e = p.epi;
+        float *warp_bias = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + 256) + (warp - 2) * kWarpBiasFloats;
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int item = blockIdx.x; item < p.num_tiles * p.splits; item += gridDim.x) {
+        // "accumulator drained" goes to the MMA thread, which in a pair lives in the leader CTA
+        const uint32_t tmem_empty_remote = kPair ? map_to_rank(smem_u32(tmem_empty), 0u) : 0u;
+        for (int item = first_item; item < p.num_tiles * p.splits; item += item_stride) {
             const int tile = item / p.splits;
             const int per_group = kGroupM * p.tiles_n;
             const int group = tile / per_group;
             const int first_m = group * kGroupM;
             const int gsize = (p.tiles_m - first_m < kGroupM) ? (p.tiles_m - first_m) : kGroupM;
             const int in_group = tile - group * per_group;
-            const int tm = first_m + in_group % gsize;
+            const int tm = kPair ? 2 * (first_m + in_group % gsize) + static_cast<int>(pair_rank) : first_m + in_group % gsize;
             const int tn = in_group / gsize;
+            // the warps that share a lane quarter split the tile's 8-column groups between them
+            constexpr int kParts = kEpiWarps / 4, kGroups = kBN / 8;
+            const int g_begin = part * kGroups / kParts, g_end = (part + 1) * kGroups / kParts;
+            const long long n0 = static_cast<long long>(tn) * kBN + g_begin * 8;
+            long long cols = p.n - n0;
+            const long long part_cols = static_cast<long long>(g_end - g_begin) * 8;
+            cols = cols < 0 ? 0 : (cols < part_cols ? cols : part_cols);
+            const int groups = static_cast<int>((cols + 7) / 8);
+            // A bias that is one value per column is fetched once per tile into the warp's slice of shared memory,
+            // before the accumulator is awaited: the loop over column groups then has no global load on its path.
+            const float *staged_bias = nullptr;
+            if (e.has_bias != 0 && e.bias_sm == 0 && e.bias_sn == 1) {
+                __syncwarp();  // every lane is done with the previous tile's values
+                for (int i = lane; i < groups * 8; i += 32) {
+                    const long long col = n0 + i;
+                    warp_bias[i] = col < p.n ? load_as_f32(e.bias, e.bias_dtype, col) : 0.0f;
+                }
+                __syncwarp();
+                staged_bias = warp_bias;
+            }
             const bool arrived = mbar_wait(tmem_full + acc, acc_phase, abort_flag, p.status, 4);
             if (threadIdx.x == 64) {
                 TC_TRACE(4);
@@ -959,14 +1106,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const bool row_ok = mi < p.m;
             const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                        static_cast<uint32_t>(acc * kBN);
-            // the warps that share a lane quarter split the tile's 8-column groups between them
-            constexpr int kParts = kEpiWarps / 4, kGroups = kBN / 8;
-            const int g_begin = part * kGroups / kParts, g_end = (part + 1) * kGroups / kParts;
-            const long long n0 = static_cast<long long>(tn) * kBN + g_begin * 8;
-            long long cols = p.n - n0;
-            const long long part_cols = static_cast<long long>(g_end - g_begin) * 8;
-            cols = cols < 0 ? 0 : (cols < part_cols ? cols : part_cols);
-            const int groups = static_cast<int>((cols + 7) / 8);
             const uint32_t taddr_part = taddr_row + static_cast<uint32_t>(g_begin * 8);
             const bool precise = e.c_dtype == KUDNN_B200_F32;
             if (p.splits > 1) {
@@ -989,33 +1128,37 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             }
             switch (e.act) {
                 case KUDNN_B200_ACT_NONE:
-                    epilogue_row<KUDNN_B200_ACT_NONE, 0>(e, taddr_part, row_ok, mi, n0, groups);
+                    epilogue_row<KUDNN_B200_ACT_NONE, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
                     break;
                 case KUDNN_B200_ACT_RELU:
-                    epilogue_row<KUDNN_B200_ACT_RELU, 0>(e, taddr_part, row_ok, mi, n0, groups);
+                    epilogue_row<KUDNN_B200_ACT_RELU, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
                     break;
                 case KUDNN_B200_ACT_SWISH:
                     if (precise) {
-                        epilogue_row<KUDNN_B200_ACT_SWISH, 1>(e, taddr_part, row_ok, mi, n0, groups);
+                        epilogue_row<KUDNN_B200_ACT_SWISH, 1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
                     } else {
-                        epilogue_row<KUDNN_B200_ACT_SWISH, 0>(e, taddr_part, row_ok, mi, n0, groups);
+                        epilogue_row<KUDNN_B200_ACT_SWISH, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
                     }
                     break;
                 case KUDNN_B200_ACT_GELU_TANH:
                     if (precise) {
-                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 1>(e, taddr_part, row_ok, mi, n0, groups);
+                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
                     } else {
-                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 0>(e, taddr_part, row_ok, mi, n0, groups);
+                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
                     }
                     break;
                 default:
-                    epilogue_row<-1, -1>(e, taddr_part, row_ok, mi, n0, groups);
+                    epilogue_row<-1, -1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
                     break;
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(tmem_empty + acc);
+                if (kPair) {
+                    mbar_arrive_cluster(tmem_empty_remote + static_cast<uint32_t>(acc * sizeof(uint64_t)));
+                } else {
+                    mbar_arrive(tmem_empty + acc);
+                }
             }
             if (threadIdx.x == 64) {
                 TC_TRACE(10);
@@ -1097,8 +1240,17 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
         __syncthreads();
     }
+    if (kPair) {
+        // neither CTA frees tensor memory or leaves while the other may still signal its barriers or, through the
+        // leader's MMAs, use its shared and tensor memory
+        cluster_sync_all();
+    }
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        if (kPair) {
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        } else {
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        }
     }
     if (threadIdx.x == 0) {
         TC_TRACE(12);
@@ -1146,7 +1298,7 @@ cudaError_t encode_kmajor(CUtensorMap *map, const void *base, int kind, long lon
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-unsigned make_idesc(int kind, int n)
+unsigned make_idesc(int kind, int n, int m_rows)
 {
     const unsigned fmt = (kind == KUDNN_B200_F32) ? 2u : (kind == KUDNN_B200_BF16 ? 1u : 0u);
     unsigned d = 0;
@@ -1154,14 +1306,14 @@ unsigned make_idesc(int kind, int n)
     d |= fmt << 7;                             // A format
     d |= fmt << 10;                            // B format
     d |= static_cast<unsigned>(n >> 3) << 17;  // N / 8
-    d |= static_cast<unsigned>(kBM >> 4) << 24;  // M / 16
+    d |= static_cast<unsigned>(m_rows >> 4) << 24;  // M / 16 (256 for a CTA pair)
     return d;                                  // both operands K-major, no negation, dense
 }
 
-template <int kKind, int kBN>
+template <int kKind, int kBN, bool kPair>
 cudaError_t launch_one(const TcPlan &plan, const TcParams &p, cudaStream_t stream)
 {
-    auto kernel = tc_linear_kernel<kKind, kBN>;
+    auto kernel = tc_linear_kernel<kKind, kBN, kPair>;
     cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem_bytes));
     if (e != cudaSuccess) {
@@ -1170,8 +1322,10 @@ cudaError_t launch_one(const TcPlan &plan, const TcParams &p, cudaStream_t strea
     CUtensorMap ta, tb;
     std::memcpy(&ta, plan.tmap_a, sizeof(ta));
     std::memcpy(&tb, plan.tmap_b, sizeof(tb));
-    if (plan.splits > 1) {
-        // the CTAs that share a tile form a cluster; blockIdx.x = tile * splits + rank
+    const int cluster = kPair ? 2 : plan.splits;
+    if (cluster > 1) {
+        // split-K: the CTAs that share a tile form a cluster, blockIdx.x = tile * splits + rank;
+        // pair mode: clusters of two, blockIdx.x = 2 * cluster + rank
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(plan.grid), 1, 1);
         cfg.blockDim = dim3(kTcThreads, 1, 1);
@@ -1179,7 +1333,7 @@ cudaError_t launch_one(const TcPlan &plan, const TcParams &p, cudaStream_t strea
         cfg.stream = stream;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = static_cast<unsigned>(plan.splits);
+        attr.val.clusterDim.x = static_cast<unsigned>(cluster);
         attr.val.clusterDim.y = 1;
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
@@ -1188,6 +1342,35 @@ cudaError_t launch_one(const TcPlan &plan, const TcParams &p, cudaStream_t strea
     }
     kernel<<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(ta, tb, p);
     return cudaGetLastError();
+}
+
+// How many clusters of two CTAs of the pair kernel the device runs at once (SMs pair up inside a GPC, so this can be
+// fewer than half the SM count).  Queried once per kernel instance.
+template <int kKind>
+int max_pair_clusters(size_t smem_bytes)
+{
+    auto kernel = tc_linear_kernel<kKind, 256, true>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)) !=
+        cudaSuccess) {
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(kTcThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return clusters;
 }
 
 }  // namespace
@@ -1216,15 +1399,29 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     if (tiles > (1ll << 30)) {
         return cudaErrorInvalidValue;
     }
+    // CTA pairs for the large-problem shape (256-wide tiles): 256 x 256 tiles over clusters of two
+    bool pair = bn == 256 && m > kBM;
+    if (const char *env = std::getenv("KUDNN_B200_TC_PAIR")) {
+        pair = pair && std::atoi(env) != 0;
+    }
+    int pair_clusters = 0;
+    if (pair) {
+        const size_t smem = static_cast<size_t>(6) * (kABytes + 128 * kStageRowBytes) + 1024 + kTailBytes;
+        pair_clusters = ops.kind == KUDNN_B200_F32   ? max_pair_clusters<KUDNN_B200_F32>(smem)
+                        : ops.kind == KUDNN_B200_F16 ? max_pair_clusters<KUDNN_B200_F16>(smem)
+                                                     : max_pair_clusters<KUDNN_B200_BF16>(smem);
+        pair = pair_clusters > 0;
+    }
+    plan->pair = pair ? 1 : 0;
     plan->block_n = bn;
-    plan->stages = (bn == 256) ? 4 : 6;
+    plan->stages = (bn == 256 && !pair) ? 4 : 6;
     // Split-K: with at most half the SMs busy and a long K, the CTAs of a cluster share a tile and cut K between
     // them (2, 4 or 8 ways: the rows of the tile are divided among the ranks for the final pass).  Each split keeps
     // at least four k-blocks so that the pipeline still fills, and no split may be empty.
     const int elems_per_row = kStageRowBytes / dtype_size(ops.kind);
     const long long num_kb = (ops.k_total + elems_per_row - 1) / elems_per_row;
     long long splits = 1;
-    if (tiles * 2 <= sm_count && num_kb >= 8) {
+    if (!pair && tiles * 2 <= sm_count && num_kb >= 8) {
         long long want = std::min<long long>(sm_count / tiles, num_kb / 4);
         if (const char *env = std::getenv("KUDNN_B200_TC_SPLITS")) {
             const long long v = std::atoll(env);
@@ -1243,13 +1440,18 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     plan->kb_per_split = static_cast<int>((num_kb + splits - 1) / splits);
     const long long items = tiles * splits;
     plan->grid = splits > 1 ? static_cast<int>(items) : static_cast<int>(tiles < sm_count ? tiles : sm_count);
-    plan->smem_bytes = static_cast<size_t>(plan->stages) * (kABytes + bn * kStageRowBytes) + 1024 + 256;
+    const int b_rows = pair ? bn / 2 : bn;  // rows of the weight operand one CTA loads per k-block
+    plan->smem_bytes = static_cast<size_t>(plan->stages) * (kABytes + b_rows * kStageRowBytes) + 1024 + kTailBytes;
+    if (pair) {
+        const long long pair_tiles = ((m + 2 * kBM - 1) / (2 * kBM)) * ((n + bn - 1) / bn);
+        plan->grid = 2 * static_cast<int>(pair_tiles < pair_clusters ? pair_tiles : pair_clusters);
+    }
     CUtensorMap ta, tb;
     cudaError_t e = encode_kmajor(&ta, ops.a, ops.kind, m, ops.k_total, ops.lda, kBM);
     if (e != cudaSuccess) {
         return e;
     }
-    e = encode_kmajor(&tb, ops.b, ops.kind, n, ops.k_total, ops.ldb, bn);
+    e = encode_kmajor(&tb, ops.b, ops.kind, n, ops.k_total, ops.ldb, b_rows);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1267,30 +1469,41 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.n = static_cast<int>(n);
     const int elems_per_row = kStageRowBytes / dtype_size(ops.kind);
     p.num_kb = static_cast<int>((ops.k_total + elems_per_row - 1) / elems_per_row);
-    p.tiles_m = static_cast<int>((m + kBM - 1) / kBM);
+    const int tile_rows = plan.pair ? 2 * kBM : kBM;
+    p.tiles_m = static_cast<int>((m + tile_rows - 1) / tile_rows);
     p.tiles_n = static_cast<int>((n + plan.block_n - 1) / plan.block_n);
     p.num_tiles = p.tiles_m * p.tiles_n;
-    p.idesc = make_idesc(ops.kind, plan.block_n);
+    p.idesc = make_idesc(ops.kind, plan.block_n, plan.pair ? 2 * kBM : kBM);
     p.status = status;
     p.splits = plan.splits;
     p.kb_per_split = plan.kb_per_split;
+    if (plan.pair) {
+        switch (ops.kind) {
+            case KUDNN_B200_F32:
+                return launch_one<KUDNN_B200_F32, 256, true>(plan, p, stream);
+            case KUDNN_B200_F16:
+                return launch_one<KUDNN_B200_F16, 256, true>(plan, p, stream);
+            default:
+                return launch_one<KUDNN_B200_BF16, 256, true>(plan, p, stream);
+        }
+    }
     if (plan.block_n == 256) {
         switch (ops.kind) {
             case KUDNN_B200_F32:
-                return launch_one<KUDNN_B200_F32, 256>(plan, p, stream);
+                return launch_one<KUDNN_B200_F32, 256, false>(plan, p, stream);
             case KUDNN_B200_F16:
-                return launch_one<KUDNN_B200_F16, 256>(plan, p, stream);
+                return launch_one<KUDNN_B200_F16, 256, false>(plan, p, stream);
             default:
-                return launch_one<KUDNN_B200_BF16, 256>(plan, p, stream);
+                return launch_one<KUDNN_B200_BF16, 256, false>(plan, p, stream);
         }
     }
     switch (ops.kind) {
         case KUDNN_B200_F32:
-            return launch_one<KUDNN_B200_F32, 128>(plan, p, stream);
+            return launch_one<KUDNN_B200_F32, 128, false>(plan, p, stream);
         case KUDNN_B200_F16:
-            return launch_one<KUDNN_B200_F16, 128>(plan, p, stream);
+            return launch_one<KUDNN_B200_F16, 128, false>(plan, p, stream);
         default:
-            return launch_one<KUDNN_B200_BF16, 128>(plan, p, stream);
+            return launch_one<KUDNN_B200_BF16, 128, false>(plan, p, stream);
     }
 }
 

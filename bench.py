@@ -319,6 +319,9 @@ def main():
     ap.add_argument("--n", type=int, default=0, help="override the column count (smaller cases for profiler captures)")
     ap.add_argument("--k", type=int, default=0, help="override the contraction length")
     ap.add_argument("--no-extras", action="store_true", help="skip the decode-GEMV, e2e and CPU legs")
+    ap.add_argument("--c5n-gather", default="fused", choices=["fused", "nccl"],
+                    help="column-sharded workload: every rank's kernel writes its slab of y into all ranks' copies "
+                         "(fused), or NCCL all-gather plus a re-stride copy after the kernel (nccl)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -361,18 +364,36 @@ def main():
     elif wname == "c5n":
         m_local = w["m"] if not args.m else args.m
         nb, n_local = kb.shard_range(n_total, world, rank, 256)
-        scaling, par = "strong", "n-sharded x%d, NCCL all-gather of y" % world
+        scaling = "strong"
+        par = "n-sharded x%d, " % world + ("the epilogue stores each slab of y into every rank's copy over NVLink"
+                                          if args.c5n_gather == "fused" else "NCCL all-gather of y + re-stride copy")
     else:
         m_local, n_local = w["m"], n_total
         scaling, par = "weak", ("replicas x%d: each GPU runs the full batch against replicated W" % world) if world > 1 \
             else "single GPU"
     x, wt, bias, res = make_inputs(w, m_local, device, seed=rank, n=n_local)
     tdt = x.dtype
-    y = torch.empty(m_local, n_local, device=device, dtype=tdt)
-    desc = make_desc(kb, w, m_local, n=n_local)
+    fused_gather = wname == "c5n" and world > 1 and args.c5n_gather == "fused"
+    peer_ptrs, y_full_ptr = [], None
+    if fused_gather:
+        # every rank holds the full [m, n_total] y in a buffer the others map; this rank's kernel writes columns
+        # [nb, nb + n_local) of all of them
+        esize = x.element_size()
+        y_full_ptr, handle = kb.peer_buffer_create(m_local * n_total * esize)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        peer_ptrs = [kb.peer_buffer_open(h) for r, h in enumerate(handles) if r != rank]
+        y = y_full_ptr + nb * esize
+        desc = make_desc(kb, w, m_local, n=n_local, ldc=n_total)
+    else:
+        y = torch.empty(m_local, n_local, device=device, dtype=tdt)
+        desc = make_desc(kb, w, m_local, n=n_local)
     lin = kb.Linear(desc)
     stream = torch.cuda.current_stream().cuda_stream
     lin.prepack(wt, stream=stream)  # weights are packed once, at set-up
+    if fused_gather:
+        mirrors = [p + nb * x.element_size() for p in peer_ptrs]
+        lin.set_mirrors(None if w["res"] else mirrors, mirrors if w["res"] else None)
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     drain_buf = torch.zeros(256 << 18, dtype=torch.float32, device=device)  # 256 MiB
 
@@ -383,7 +404,7 @@ def main():
         drain_buf.sum()
 
     gathered = None
-    if wname == "c5n" and world > 1:
+    if wname == "c5n" and world > 1 and not fused_gather:
         gathered = torch.empty(world * m_local, n_local, device=device, dtype=tdt)
         y_full = torch.empty(m_local, n_total, device=device, dtype=tdt)
 

@@ -148,6 +148,25 @@ KUDNN_B200_API int kudnn_b200_linear_run_static_scratch(const kudnn_b200_linear_
 /* Reads the device-side status word of the handle (bounded waits that gave up) after synchronising the stream. */
 KUDNN_B200_API int kudnn_b200_linear_check(kudnn_b200_linear_t handle, void *cuda_stream);
 
+/* ---- column-sharded layers: one kernel computes a slab of y and writes it into every rank's copy -------------------
+ * No counterpart in the reference (a single-socket CPU library; its tensor-parallel users gather outside of it).
+ *
+ * set_mirrors: from now on every run of the handle stores c (and out) not only through args.c / args.out but also
+ * through each mirror pointer, with the same strides.  A mirror is typically the same tensor in another GPU's
+ * memory, opened with kudnn_b200_peer_buffer_open; the stores go over NVLink from the kernel's epilogue, tile by
+ * tile, so there is no gather step afterwards.  Up to 7 mirrors; each must be 16-byte congruent with the primary
+ * pointer.  Pass count = 0 to switch mirroring off.  When a launch has completed on a rank (stream synchronised),
+ * its slab is complete in every mirror; the ranks still have to tell each other (a barrier) before they read. */
+KUDNN_B200_API int kudnn_b200_linear_set_mirrors(kudnn_b200_linear_t handle, int count, void *const *c_mirrors,
+                                                 void *const *out_mirrors);
+
+/* A device buffer other processes of this machine can map, and its 64-byte handle; open / close on the other side. */
+#define KUDNN_B200_PEER_HANDLE_BYTES 64
+KUDNN_B200_API int kudnn_b200_peer_buffer_create(size_t bytes, void **dev_ptr, unsigned char *handle_out);
+KUDNN_B200_API int kudnn_b200_peer_buffer_open(const unsigned char *handle, void **dev_ptr);
+KUDNN_B200_API int kudnn_b200_peer_buffer_close(void *dev_ptr);
+KUDNN_B200_API int kudnn_b200_peer_buffer_destroy(void *dev_ptr);
+
 /* Introspection used by tests and the benchmark. */
 KUDNN_B200_API int kudnn_b200_linear_force_kernel(kudnn_b200_linear_t handle, int kernel);
 KUDNN_B200_API int kudnn_b200_linear_last_kernel(kudnn_b200_linear_t handle);

@@ -11,6 +11,7 @@ from .capi import (  # noqa: F401
     KERNEL_AUTO, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_GEMV_RING, KERNEL_SIMT, KERNEL_TC, KERNEL_NAMES,
     RES_ELTWISE_MUL, RES_EXT, RES_IDENTICAL, RES_NONE,
     KudnnError, Linear, LinearDesc, library, library_path, make_desc, run_static_scratch, shard_range,
+    peer_buffer_close, peer_buffer_create, peer_buffer_destroy, peer_buffer_open,
 )
 
 __all__ = [
@@ -19,4 +20,5 @@ __all__ = [
     "KERNEL_AUTO", "KERNEL_GEMV_FMA", "KERNEL_GEMV_MMA", "KERNEL_GEMV_RING", "KERNEL_SIMT", "KERNEL_TC", "KERNEL_NAMES",
     "RES_ELTWISE_MUL", "RES_EXT", "RES_IDENTICAL", "RES_NONE",
     "KudnnError", "Linear", "LinearDesc", "library", "library_path", "make_desc", "run_static_scratch", "shard_range",
+    "peer_buffer_close", "peer_buffer_create", "peer_buffer_destroy", "peer_buffer_open",
 ]

@@ -60,7 +60,8 @@ EXPORTS = [
     "kudnn_b200_linear_run_static_scratch", "kudnn_b200_linear_run_any",
     "kudnn_b200_linear_force_kernel", "kudnn_b200_linear_last_kernel", "kudnn_b200_linear_last_launches",
     "kudnn_b200_linear_workspace_bytes", "kudnn_b200_shard_range", "kudnn_b200_last_error", "kudnn_b200_version",
-    "kudnn_b200_device_count",
+    "kudnn_b200_device_count", "kudnn_b200_linear_set_mirrors", "kudnn_b200_peer_buffer_create",
+    "kudnn_b200_peer_buffer_open", "kudnn_b200_peer_buffer_close", "kudnn_b200_peer_buffer_destroy",
 ]
 
 _lib = None
@@ -91,6 +92,11 @@ def library():
     lib.kudnn_b200_linear_check.argtypes = [vp, vp]
     lib.kudnn_b200_linear_run_any.argtypes = [vp, ctypes.POINTER(LinearArgs), vp]
     lib.kudnn_b200_linear_run_static_scratch.argtypes = [ctypes.POINTER(LinearDesc), ctypes.POINTER(LinearArgs), vp]
+    lib.kudnn_b200_linear_set_mirrors.argtypes = [vp, i32, ctypes.POINTER(vp), ctypes.POINTER(vp)]
+    lib.kudnn_b200_peer_buffer_create.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp), ctypes.c_char_p]
+    lib.kudnn_b200_peer_buffer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    lib.kudnn_b200_peer_buffer_close.argtypes = [vp]
+    lib.kudnn_b200_peer_buffer_destroy.argtypes = [vp]
     lib.kudnn_b200_linear_force_kernel.argtypes = [vp, i32]
     lib.kudnn_b200_linear_last_kernel.argtypes = [vp]
     lib.kudnn_b200_linear_last_launches.argtypes = [vp]
@@ -166,6 +172,32 @@ def shard_range(total, nparts, part, align=1):
     return b.value, c.value
 
 
+PEER_HANDLE_BYTES = 64
+
+
+def peer_buffer_create(nbytes):
+    """A device buffer other processes on this machine can map.  Returns (device pointer, 64-byte handle)."""
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(PEER_HANDLE_BYTES)
+    _check(library().kudnn_b200_peer_buffer_create(nbytes, ctypes.byref(ptr), handle))
+    return ptr.value, handle.raw
+
+
+def peer_buffer_open(handle):
+    """Maps a buffer another process created with peer_buffer_create; returns its device pointer in this process."""
+    ptr = ctypes.c_void_p()
+    _check(library().kudnn_b200_peer_buffer_open(bytes(handle), ctypes.byref(ptr)))
+    return ptr.value
+
+
+def peer_buffer_close(ptr):
+    _check(library().kudnn_b200_peer_buffer_close(ptr))
+
+
+def peer_buffer_destroy(ptr):
+    _check(library().kudnn_b200_peer_buffer_destroy(ptr))
+
+
 def run_static_scratch(desc, a, b, c=None, bias=None, res=None, out=None, alpha=1.0, beta=0.0, gamma=1.0, stream=None):
     """Decode-shaped Linear (m <= 16) through the entry point that allocates no device memory.
 
@@ -226,6 +258,17 @@ class Linear:
 
     def force_kernel(self, kernel):
         _check(self._lib.kudnn_b200_linear_force_kernel(self._h, kernel))
+
+    def set_mirrors(self, c_mirrors=None, out_mirrors=None):
+        """Every later run also stores c / out through these device pointers (tensors or integers), same strides:
+        the same output tensor in other GPUs' memory, for column-sharded layers.  Empty or None switches it off."""
+        cm = [_ptr(p) for p in (c_mirrors or [])]
+        om = [_ptr(p) for p in (out_mirrors or [])]
+        count = max(len(cm), len(om))
+        arr_t = ctypes.c_void_p * max(count, 1)
+        ca = arr_t(*(cm + [None] * (count - len(cm))))
+        oa = arr_t(*(om + [None] * (count - len(om))))
+        _check(self._lib.kudnn_b200_linear_set_mirrors(self._h, count, ca, oa))
 
     @property
     def last_kernel(self):

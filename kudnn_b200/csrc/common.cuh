@@ -28,6 +28,8 @@ struct DeviceStatus {
     int pad;
 };
 
+constexpr int kMaxMirrors = 7;
+
 struct EpiParams {
     void *c;
     const void *bias;
@@ -38,7 +40,15 @@ struct EpiParams {
     int c_dtype, bias_dtype, res_dtype, out_dtype;
     int has_bias, act, res_op;
     int m, n;
+    // Mirrors: further copies of the outputs (same strides), e.g. the same tensor in every peer GPU's memory, written
+    // by the same stores.  Byte distance of each mirror from c / out.
+    int n_mirrors;
+    long long c_delta[kMaxMirrors], out_delta[kMaxMirrors];
 };
+
+// Writes v (exactly representable in dtype) to base[idx] and to the same element of every mirror.
+__device__ __forceinline__ void store_exact_mirrored(void *base, int dtype, long long idx, float v, int n_mirrors,
+                                                     const long long *delta);
 
 __device__ __forceinline__ float bf16_bits_to_f32(unsigned short h)
 {
@@ -99,6 +109,15 @@ __device__ __forceinline__ void store_exact(void *p, int dtype, long long idx, f
         static_cast<unsigned short *>(p)[idx] = f32_to_f16_rne_bits(v);
     } else {
         static_cast<unsigned short *>(p)[idx] = static_cast<unsigned short>(__float_as_uint(v) >> 16);
+    }
+}
+
+__device__ __forceinline__ void store_exact_mirrored(void *base, int dtype, long long idx, float v, int n_mirrors,
+                                                     const long long *delta)
+{
+    store_exact(base, dtype, idx, v);
+    for (int i = 0; i < n_mirrors; ++i) {
+        store_exact(static_cast<char *>(base) + delta[i], dtype, idx, v);
     }
 }
 
@@ -231,10 +250,10 @@ __device__ __forceinline__ void epilogue_scalar(const EpiParams &p, float acc, l
     }
     EpiResult r = finish_element(p, acc, c_old, bias, res);
     if (p.c != nullptr) {
-        store_exact(p.c, p.c_dtype, ic, r.c);
+        store_exact_mirrored(p.c, p.c_dtype, ic, r.c, p.n_mirrors, p.c_delta);
     }
     if (p.res_op != KUDNN_B200_RES_NONE) {
-        store_exact(p.out, p.out_dtype, mi * p.out_sm + ni * p.out_sn, r.out);
+        store_exact_mirrored(p.out, p.out_dtype, mi * p.out_sm + ni * p.out_sn, r.out, p.n_mirrors, p.out_delta);
     }
 }
 

@@ -103,6 +103,11 @@ struct kudnn_b200_linear_s {
     int sm_count = 0;
     std::mutex lock;
 
+    // output mirrors (kudnn_b200_linear_set_mirrors): device pointers to further copies of c / out
+    int n_mirrors = 0;
+    void *c_mirror[kb::kMaxMirrors] = {};
+    void *out_mirror[kb::kMaxMirrors] = {};
+
     DeviceBuffer status;        // kb::DeviceStatus
     DeviceBuffer gemv_partials, gemv_counters;
     DeviceBuffer a_scratch;     // per-call packed activations
@@ -197,6 +202,7 @@ void fill_epi(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, 
     e->res_op = d.res_op;
     e->m = static_cast<int>(d.m);
     e->n = static_cast<int>(d.n);
+    e->n_mirrors = 0;
 }
 
 void fill_problem(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, kb::LinearProblem *p)
@@ -364,6 +370,21 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
 
     kb::LinearProblem pr;
     fill_problem(d, args, &pr);
+    if (h->n_mirrors > 0) {
+        // the kernels address a mirror as "primary pointer + byte distance", which also survives batch offsets
+        pr.epi.n_mirrors = h->n_mirrors;
+        for (int i = 0; i < h->n_mirrors; ++i) {
+            pr.epi.c_delta[i] = args.c != nullptr ? static_cast<char *>(h->c_mirror[i]) - static_cast<char *>(args.c) : 0;
+            pr.epi.out_delta[i] =
+                args.out != nullptr ? static_cast<char *>(h->out_mirror[i]) - static_cast<char *>(args.out) : 0;
+            if ((args.c != nullptr && (h->c_mirror[i] == nullptr || pr.epi.c_delta[i] % 16 != 0)) ||
+                (d.res_op != KUDNN_B200_RES_NONE && (h->out_mirror[i] == nullptr || pr.epi.out_delta[i] % 16 != 0))) {
+                return fail(KUDNN_B200_BAD_ARGUMENTS,
+                            "run: every mirror needs a pointer for each output that is written, at a distance from "
+                            "the primary output that is a multiple of 16 bytes");
+            }
+        }
+    }
     int launches = 0;
     const int forced = h->forced_kernel;
     const bool use_packed = (h->packed_key != nullptr && h->packed_key == args.b);
@@ -1077,6 +1098,20 @@ int kudnn_b200_linear_force_kernel(kudnn_b200_linear_t h, int kernel)
         return fail(KUDNN_B200_BAD_ARGUMENTS, "force_kernel: bad argument");
     }
     h->forced_kernel = kernel;
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_set_mirrors(kudnn_b200_linear_t h, int count, void *const *c_mirrors, void *const *out_mirrors)
+{
+    if (h == nullptr || count < 0 || count > kb::kMaxMirrors) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "set_mirrors: count must be between 0 and %d", kb::kMaxMirrors);
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    h->n_mirrors = count;
+    for (int i = 0; i < count; ++i) {
+        h->c_mirror[i] = c_mirrors != nullptr ? c_mirrors[i] : nullptr;
+        h->out_mirror[i] = out_mirrors != nullptr ? out_mirrors[i] : nullptr;
+    }
     return KUDNN_B200_OK;
 }
 

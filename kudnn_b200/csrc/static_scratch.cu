@@ -147,6 +147,7 @@ extern "C" int kudnn_b200_linear_run_static_scratch(const kudnn_b200_linear_desc
     e.has_bias = d.has_bias;
     e.act = d.act;
     e.res_op = d.res_op;
+    e.n_mirrors = 0;
     e.m = static_cast<int>(d.m);
     e.n = static_cast<int>(d.n);
     pr.batch.n1 = 1;

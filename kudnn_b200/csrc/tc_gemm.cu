@@ -30,6 +30,8 @@
 #include <cstring>
 #include <mutex>
 
+// Optional phase timestamps for tuning (build with -DKUDNN_B200_TC_TRACE): a few threads per CTA write %globaltimer
+// at role boundaries into a device array that kudnn_b200_debug_tc_trace copies out.  Not part of the product build.
 #ifdef KUDNN_B200_TC_TRACE
 __device__ long long g_tc_trace[160 * 16];
 #define TC_TRACE(slot)                                                                             \
@@ -450,6 +452,9 @@ __device__ __forceinline__ void epilogue_group8(const EpiParams &e, const uint32
     }
     if (e.c != nullptr) {
         store8(e.c, ct, ic, e.c_sn, c_vec, valid, v);
+        for (int i = 0; i < e.n_mirrors; ++i) {
+            store8(static_cast<char *>(e.c) + e.c_delta[i], ct, ic, e.c_sn, c_vec, valid, v);
+        }
     }
     if (e.res_op != KUDNN_B200_RES_NONE) {
         const long long ir = mi * e.res_sm + ni * e.res_sn;
@@ -483,7 +488,11 @@ __device__ __forceinline__ void epilogue_group8(const EpiParams &e, const uint32
             }
         }
         const long long io = mi * e.out_sm + ni * e.out_sn;
-        store8(e.out, ot, io, e.out_sn, full8 && vec_ok(e.out, ot, io, e.out_sn), valid, v);
+        const bool out_vec = full8 && vec_ok(e.out, ot, io, e.out_sn);
+        store8(e.out, ot, io, e.out_sn, out_vec, valid, v);
+        for (int i = 0; i < e.n_mirrors; ++i) {
+            store8(static_cast<char *>(e.out) + e.out_delta[i], ot, io, e.out_sn, out_vec, valid, v);
+        }
     }
 }
 
@@ -640,6 +649,9 @@ __device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const u
     }
     if (rp.c != nullptr) {
         store8_vec(rp.c + byte_off_c, ct, v);
+        for (int i = 0; i < e.n_mirrors; ++i) {
+            store8_vec(rp.c + e.c_delta[i] + byte_off_c, ct, v);
+        }
     }
     if (e.res_op != KUDNN_B200_RES_NONE) {
         load8_vec(rp.res + byte_off_res, e.res_dtype, side);
@@ -666,6 +678,9 @@ __device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const u
             round_rne8<KUDNN_B200_BF16>(v);
         }
         store8_vec(rp.out + byte_off_out, ot, v);
+        for (int i = 0; i < e.n_mirrors; ++i) {
+            store8_vec(rp.out + e.out_delta[i] + byte_off_out, ot, v);
+        }
     }
 }
 

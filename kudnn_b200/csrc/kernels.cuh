@@ -75,12 +75,14 @@ struct TcPlan {
     // `splits` CTAs, grid = tiles * splits
     int splits, kb_per_split;
     int pair;      // 1: clusters of two CTAs share 256 x block_n tiles (cta_group::2)
+    int narrow_from;  // pair mode: tiles from this index on are processed as two pieces of half the width
     unsigned char tmap_a[128] __attribute__((aligned(64)));
     unsigned char tmap_b[128] __attribute__((aligned(64)));
 };
 bool tc_available();
 const char *tc_unavailable_reason();
-cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm_count, TcPlan *plan);
+// with_staging: the launch writes output mirrors and needs the epilogue's row staging in shared memory
+cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm_count, bool with_staging, TcPlan *plan);
 cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams &epi, long long m, long long n,
                       DeviceStatus *status, cudaStream_t stream);
 

@@ -126,6 +126,7 @@ struct kudnn_b200_linear_s {
     kb::TcPlan tc_plan;
     const void *plan_a = nullptr, *plan_b = nullptr;
     long long plan_m = 0;
+    bool plan_staging = false;
     bool plan_valid = false;
 
     // host-pointer path: copy-in, compute and copy-out streams with one event pair per row chunk
@@ -527,22 +528,24 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
                 ops.a = h->a_scratch.ptr;
                 ops.lda = pitch;
             }
-            if (!(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b && h->plan_m == d.m)) {
-                cudaError_t e = kb::tc_make_plan(ops, d.m, d.n, h->sm_count, &h->tc_plan);
+            const bool staging = pr.epi.n_mirrors > 0;
+            if (!(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b && h->plan_m == d.m && h->plan_staging == staging)) {
+                cudaError_t e = kb::tc_make_plan(ops, d.m, d.n, h->sm_count, staging, &h->tc_plan);
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "tensor map encoding");
                 }
                 h->plan_a = ops.a;
                 h->plan_b = ops.b;
                 h->plan_m = d.m;
+                h->plan_staging = staging;
                 h->plan_valid = true;
                 if (const char *dbg = std::getenv("KUDNN_B200_DEBUG")) {
                     if (*dbg != '\0' && *dbg != '0') {
                         std::fprintf(stderr, "kudnn_b200: tensor-core plan m=%lld n=%lld k=%lld: tile %s x %d, %d stages, grid %d, "
-                                             "k splits %d, %zu bytes of shared memory\n",
+                                             "k splits %d, narrow tail from tile %d, %zu bytes of shared memory\n",
                                      static_cast<long long>(d.m), static_cast<long long>(d.n), static_cast<long long>(d.k),
                                      h->tc_plan.pair ? "256 (CTA pair)" : "128", h->tc_plan.block_n, h->tc_plan.stages,
-                                     h->tc_plan.grid, h->tc_plan.splits, h->tc_plan.smem_bytes);
+                                     h->tc_plan.grid, h->tc_plan.splits, h->tc_plan.pair ? h->tc_plan.narrow_from : -1, h->tc_plan.smem_bytes);
                     }
                 }
             }

@@ -4,15 +4,19 @@
 // (src/dnn/src/matmul_jit/MatrixComputation/kudnn_default_impl_fp16fp16f32f32.cpp:900-983) and the BLAS calls of
 // src/dnn/src/kudnn_gemm.cpp:157-227.
 //
-// Shape of one CTA (448 threads, persistent over output tiles, one CTA per SM):
-//   warp 0      producer: one lane issues the TMA loads of the A tile [128 x 128 B] and the B tile [BN x 128 B]
-//               of every k-block into the ring (4 or 6 stages), 128-byte swizzle, completion on an mbarrier
-//   warp 1      one lane issues tcgen05.mma (M=128, N=BN, K=32 bytes per instruction, four per k-block) into one
-//               of two TMEM accumulators and commits to the stage's "empty" barrier / the tile's "full" barrier;
-//               the warp also owns TMEM allocation
-//   warps 2..13 epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; three warps share a lane quarter and
-//               split the columns) 8 columns at a time, applies the post-GEMM chain and stores 16-byte vectors;
-//               the second accumulator lets this overlap the next tile's main loop
+// Shape of one CTA (320 threads, persistent over output tiles, one CTA per SM):
+//   warp 0      producer: one lane issues the TMA loads of the A tile [128 x 128 B] and the B tile [rows x 128 B]
+//               of every k-block into the ring (3 or 5 stages), 128-byte swizzle, completion on an mbarrier
+//   warp 1      one lane issues tcgen05.mma (K = 32 bytes per instruction, four per k-block) into one of two TMEM
+//               accumulators and commits to the stage's "empty" barrier / the tile's "full" barrier; the warp also
+//               owns TMEM allocation
+//   warps 2..9  epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; two warps share a lane quarter and
+//               split the columns) 8 columns at a time, applies the post-GEMM chain, collects 128 bytes per row in
+//               shared memory of its own and stores them so that an instruction covers 4 rows x 128 bytes; the
+//               second accumulator lets this overlap the next tile's main loop
+// Three launch shapes (tc_make_plan): clusters of two CTAs on 256 x 256 tiles with cta_group::2 MMAs (large
+// problems), single CTAs on 128 x 256 / 128 x 128 tiles, and clusters of 2-8 CTAs that cut K of one 128 x 128 tile
+// and add their partial tiles through distributed shared memory (few tiles, long K).
 // Operands are K-major ([rows, k], k contiguous).  16-bit inputs run as kind::f16 with fp32 accumulation.  fp32
 // inputs run as kind::tf32 on split planes: x = hi + lo with hi = tf32(x), and the packed operands
 // A' = [a_lo | a_hi | a_hi], B' = [b_hi | b_lo | b_hi] make one pass over 3k compute a_lo.b_hi + a_hi.b_lo + a_hi.b_hi.
@@ -59,8 +63,12 @@ constexpr int kStageRowBytes = 128;  // one swizzle row: 64 16-bit or 32 32-bit 
 constexpr int kABytes = kBM * kStageRowBytes;
 constexpr int kGroupM = 16;  // tile rows per raster group
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about two seconds at 2 GHz
-constexpr int kWarpBiasFloats = 96;  // per epilogue warp: the bias values of its columns of the current tile, as fp32
-constexpr int kTailBytes = 256 + kEpiWarps * kWarpBiasFloats * 4;  // barriers and flags, then the bias slices
+constexpr int kWarpBiasFloats = 128;  // per epilogue warp: the bias values of its columns of the current tile, as fp32
+constexpr int kWarpStageBytes = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes of output on their way to memory
+// after the stage ring: barriers and flags (256 bytes), the bias slices; then, if present, the output staging
+constexpr int kTailBytes = 256 + kEpiWarps * kWarpBiasFloats * 4;
+constexpr int kStagingBytes = kEpiWarps * kWarpStageBytes;  // only launches with output mirrors carry it (one stage less)
+constexpr int kMaxStages = 6;
 
 struct TcParams {
     EpiParams epi;
@@ -72,6 +80,11 @@ struct TcParams {
     // split-K for problems with fewer tiles than SMs: the `splits` CTAs of a thread-block cluster share one tile,
     // each contracts over kb_per_split k-blocks, and the partial tiles are added through distributed shared memory
     int splits, kb_per_split;
+    int stages;  // depth of the shared-memory ring
+    // CTA pairs: work items [0, narrow_from) are whole 256 x BN tiles; each later tile is two items of half the width,
+    // so that a last wave that would keep fewer than half the pairs busy is spread over twice as many
+    int num_items, narrow_from;
+    unsigned idesc_narrow;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -573,15 +586,15 @@ __device__ __forceinline__ void round_rne8(float (&v)[8])
     }
 }
 
-// Fast form of epilogue_group8: beta == 0, every tensor contiguous along the row and 16-byte aligned at this group,
-// all 8 columns in range.  Same arithmetic, no address arithmetic beyond pointer bumps.
+// Arithmetic of the fast form of epilogue_group8 (beta == 0, side inputs contiguous along the row and 16-byte
+// aligned at this group, all 8 columns in range), first half: v receives the 8 values of c, exactly representable
+// in c's type.
 template <int kAct, int kPrecise>
-__device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const uint32_t (&raw)[8], const RowPointers &rp,
-                                                     int byte_off_c, int byte_off_bias, int byte_off_res, int byte_off_out,
-                                                     int g)
+__device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32_t (&raw)[8], const RowPointers &rp,
+                                                int byte_off_bias, int g, float (&v)[8])
 {
     const int ct = e.c_dtype;
-    float v[8], side[8];
+    float side[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         v[j] = __uint_as_float(raw[j]);
@@ -647,39 +660,57 @@ __device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const u
             }
         }
     }
+}
+
+// Second half: v holds the values of c and is replaced by those of the second output (c (+) res).
+__device__ __forceinline__ void compute_out8_fast(const EpiParams &e, const RowPointers &rp, int byte_off_res, float (&v)[8])
+{
+    float side[8];
+    load8_vec(rp.res + byte_off_res, e.res_dtype, side);
+    if (e.res_op == KUDNN_B200_RES_IDENTICAL) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] += side[j];
+        }
+    } else if (e.res_op == KUDNN_B200_RES_EXT) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] = fmaf(side[j], e.gamma, v[j]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] *= side[j];
+        }
+    }
+    const int ot = e.out_dtype;
+    if (ot == KUDNN_B200_F16) {
+        round_rne8<KUDNN_B200_F16>(v);
+    } else if (ot == KUDNN_B200_BF16) {
+        round_rne8<KUDNN_B200_BF16>(v);
+    }
+}
+
+// Fast form of epilogue_group8: same arithmetic, no address arithmetic beyond pointer bumps, one 16-byte (fp32: two)
+// store per tensor and mirror.
+template <int kAct, int kPrecise>
+__device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const uint32_t (&raw)[8], const RowPointers &rp,
+                                                     int byte_off_c, int byte_off_bias, int byte_off_res, int byte_off_out,
+                                                     int g)
+{
+    float v[8];
+    compute_c8_fast<kAct, kPrecise>(e, raw, rp, byte_off_bias, g, v);
     if (rp.c != nullptr) {
-        store8_vec(rp.c + byte_off_c, ct, v);
+        store8_vec(rp.c + byte_off_c, e.c_dtype, v);
         for (int i = 0; i < e.n_mirrors; ++i) {
-            store8_vec(rp.c + e.c_delta[i] + byte_off_c, ct, v);
+            store8_vec(rp.c + e.c_delta[i] + byte_off_c, e.c_dtype, v);
         }
     }
     if (e.res_op != KUDNN_B200_RES_NONE) {
-        load8_vec(rp.res + byte_off_res, e.res_dtype, side);
-        if (e.res_op == KUDNN_B200_RES_IDENTICAL) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[j] += side[j];
-            }
-        } else if (e.res_op == KUDNN_B200_RES_EXT) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[j] = fmaf(side[j], e.gamma, v[j]);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[j] *= side[j];
-            }
-        }
-        const int ot = e.out_dtype;
-        if (ot == KUDNN_B200_F16) {
-            round_rne8<KUDNN_B200_F16>(v);
-        } else if (ot == KUDNN_B200_BF16) {
-            round_rne8<KUDNN_B200_BF16>(v);
-        }
-        store8_vec(rp.out + byte_off_out, ot, v);
+        compute_out8_fast(e, rp, byte_off_res, v);
+        store8_vec(rp.out + byte_off_out, e.out_dtype, v);
         for (int i = 0; i < e.n_mirrors; ++i) {
-            store8_vec(rp.out + e.out_delta[i] + byte_off_out, ot, v);
+            store8_vec(rp.out + e.out_delta[i] + byte_off_out, e.out_dtype, v);
         }
     }
 }
@@ -693,6 +724,110 @@ __device__ __forceinline__ bool row_contiguous_aligned(const void *base, int dty
 // taddr.  The loop is rolled to keep the code small (a fully unrolled epilogue does not fit the instruction cache
 // and runs an order of magnitude slower); the TMEM load of the next group is in flight while the current one is
 // processed.  Rows whose tensors are contiguous and 16-byte aligned take the pointer-bumping fast path.
+// ---- row-coalesced output ---------------------------------------------------------------------------------------
+// A TMEM lane is a row, so a thread's natural store is 16 bytes of its own row and a warp's store instruction touches
+// 32 rows.  When a whole warp takes the vector path and one output tensor is written, the warp instead collects 128
+// bytes per row (8 column groups of a 16-bit type, 4 of fp32) in 4 KiB of shared memory of its own and writes them
+// out with every instruction covering 4 rows x 128 contiguous bytes.  That is what memory, and above all a peer GPU
+// behind NVLink (mirrors), wants to see.  Chunks of 16 bytes are swizzled with the row index so that both the
+// row-wise writes and the chunk-wise reads are free of bank conflicts.  No barrier beyond __syncwarp is involved.
+__device__ __forceinline__ void pack8_to_chunks(const float (&v)[8], int dtype, uint4 &lo, uint4 &hi)
+{
+    if (dtype == KUDNN_B200_F32) {
+        lo = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+        hi = make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7]));
+    } else {
+        unsigned w[4];
+        if (dtype == KUDNN_B200_BF16) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[j] = (__float_as_uint(v[2 * j]) >> 16) | (__float_as_uint(v[2 * j + 1]) & 0xffff0000u);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<const unsigned *>(&h);
+            }
+        }
+        lo = make_uint4(w[0], w[1], w[2], w[3]);
+        hi = lo;
+    }
+}
+
+template <int kAct, int kPrecise>
+__device__ __noinline__ void epilogue_rows_coalesced(const EpiParams &e, uint32_t taddr, int groups, const RowPointers rp,
+                                                        unsigned char *stage, int lane)
+{
+    // the one output tensor that is written: c, or the second output when c is not requested
+    const bool second = rp.c == nullptr;
+    const int odt = second ? e.out_dtype : e.c_dtype;
+    const int chunks_per_group = (odt == KUDNN_B200_F32) ? 2 : 1;
+    const int groups_per_pass = 8 / chunks_per_group;
+    const long long pitch = (second ? e.out_sm : e.c_sm) * dtype_size(odt);  // bytes between rows
+    char *row0 = (second ? rp.out : rp.c) - static_cast<long long>(lane) * pitch;  // row of lane 0
+    const long long *delta = second ? e.out_delta : e.c_delta;
+    const int step_bias = 8 * dtype_size(e.bias_dtype), step_res = 8 * dtype_size(e.res_dtype);
+    const uint32_t stage_addr = smem_u32(stage);
+    const uint32_t my_row = stage_addr + static_cast<uint32_t>(lane * 128);
+
+    uint32_t next[8], cur[8];
+    tmem_load_8_issue(taddr, next);
+    for (int g0 = 0; g0 < groups; g0 += groups_per_pass) {
+        const int pass_groups = (groups - g0 < groups_per_pass) ? groups - g0 : groups_per_pass;
+#pragma unroll 1
+        for (int gi = 0; gi < pass_groups; ++gi) {
+            const int g = g0 + gi;
+            tmem_load_wait(next);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                cur[j] = next[j];
+            }
+            if (g + 1 < groups) {
+                tmem_load_8_issue(taddr + static_cast<uint32_t>((g + 1) * 8), next);
+            }
+            float v[8];
+            compute_c8_fast<kAct, kPrecise>(e, cur, rp, g * step_bias, g, v);
+            if (second) {
+                compute_out8_fast(e, rp, g * step_res, v);
+            }
+            uint4 lo, hi;
+            pack8_to_chunks(v, odt, lo, hi);
+            const int c0 = gi * chunks_per_group;
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + static_cast<uint32_t>(((c0 ^ (lane & 7)) << 4))),
+                         "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w)
+                         : "memory");
+            if (chunks_per_group == 2) {
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
+                                 my_row + static_cast<uint32_t>((((c0 + 1) ^ (lane & 7)) << 4))),
+                             "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                             : "memory");
+            }
+        }
+        __syncwarp();
+        // 8 lanes per row, 4 rows per instruction
+        const int chunk = lane & 7;
+        const int valid_chunks = pass_groups * chunks_per_group;
+        const long long col_bytes = static_cast<long long>(g0) * 8 * dtype_size(odt) + chunk * 16;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int r = j * 4 + (lane >> 3);
+            if (chunk < valid_chunks) {
+                uint4 v;
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                             : "r"(stage_addr + static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4))));
+                char *dst = row0 + r * pitch + col_bytes;
+                *reinterpret_cast<uint4 *>(dst) = v;
+                for (int i = 0; i < e.n_mirrors; ++i) {
+                    *reinterpret_cast<uint4 *>(dst + delta[i]) = v;
+                }
+            }
+        }
+        __syncwarp();  // the rows are reused by the next pass
+    }
+}
+
 // Row-base pointers for the vector path of the epilogue.  Returns whether that path applies to the `groups` groups
 // of 8 columns starting at (mi, n0): whole groups inside n, no beta term, every tensor involved contiguous along n
 // and 16-byte aligned there.
@@ -738,7 +873,7 @@ __device__ __forceinline__ bool setup_row_pointers(const EpiParams &e, bool row_
 
 template <int kAct, int kPrecise>
 __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr, bool row_ok, long long mi, long long n0,
-                                             int groups, const float *staged_bias)
+                                             int groups, const float *staged_bias, unsigned char *stage, int lane)
 {
     if (groups <= 0) {
         return;
@@ -748,6 +883,12 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
     if (staged_bias != nullptr && rp.bias_mode == 1) {
         rp.bias_mode = 3;
         rp.bias_smem = staged_bias;
+    }
+    // all 32 rows on the vector path and a single output tensor: collect 128-byte row pieces and store those
+    const bool one_output = (rp.c != nullptr) != (e.res_op != KUDNN_B200_RES_NONE);
+    if (stage != nullptr && __all_sync(0xffffffffu, fast && one_output)) {
+        epilogue_rows_coalesced<kAct, kPrecise>(e, taddr, groups, rp, stage, lane);
+        return;
     }
     const int step_c = 8 * dtype_size(e.c_dtype), step_bias = 8 * dtype_size(e.bias_dtype);
     const int step_res = 8 * dtype_size(e.res_dtype), step_out = 8 * dtype_size(e.out_dtype);
@@ -880,6 +1021,26 @@ __device__ __forceinline__ void finish_split_rows(const EpiParams &e, const floa
     }
 }
 
+// Work item -> tile index, column offset inside the tile and width of the piece.
+template <bool kPair, int kBN>
+__device__ __forceinline__ void decode_item(const TcParams &p, int item, int &tile, int &n_off, int &width)
+{
+    if (!kPair) {
+        tile = item / p.splits;
+        n_off = 0;
+        width = kBN;
+    } else if (item < p.narrow_from) {
+        tile = item;
+        n_off = 0;
+        width = kBN;
+    } else {
+        const int j = item - p.narrow_from;
+        tile = p.narrow_from + (j >> 1);
+        n_off = (j & 1) * (kBN / 2);
+        width = kBN / 2;
+    }
+}
+
 // kPair: two CTAs (a cluster of two SMs) work on a 256 x kBN tile with cta_group::2 MMAs.  Each CTA loads its 128
 // rows of A and half of the B rows, so a k-block costs an SM 32 KiB of L2 traffic instead of the 48 KiB of the
 // single-CTA 128 x 256 tile; the single-CTA kernel is limited by exactly that traffic.  Rank 0 of the pair (the
@@ -892,7 +1053,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     constexpr int kBRows = kPair ? kBN / 2 : kBN;  // rows of B this CTA loads per k-block
     constexpr int kBBytes = kBRows * kStageRowBytes;
     constexpr int kStageBytes = kABytes + kBBytes;
-    constexpr int kStages = (kBRows == 256) ? 4 : 6;
+    const int kStages = p.stages;  // 3-6, what fits beside the tail (and the output staging when mirrors are written)
     constexpr int kTmemCols = 2 * kBN;
     constexpr int kElemsPerRow = (kKind == KUDNN_B200_F32) ? 32 : 64;  // elements per 128-byte k-block row
 
@@ -902,10 +1063,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                                                             ~static_cast<uintptr_t>(1023u));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
     uint64_t *full_bar = bars;
-    uint64_t *empty_bar = bars + kStages;
-    uint64_t *tmem_full = bars + 2 * kStages;
-    uint64_t *tmem_empty = bars + 2 * kStages + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 4);
+    uint64_t *empty_bar = bars + kMaxStages;
+    uint64_t *tmem_full = bars + 2 * kMaxStages;
+    uint64_t *tmem_empty = bars + 2 * kMaxStages + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kMaxStages + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -964,8 +1125,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             int stage = 0;
             uint32_t phase = 0;
             bool alive = true;
-            for (int item = first_item; alive && item < p.num_tiles * p.splits; item += item_stride) {
-                const int tile = item / p.splits, split = item - tile * p.splits;
+            for (int item = first_item; alive && item < p.num_items; item += item_stride) {
+                int tile, n_off, width;
+                decode_item<kPair, kBN>(p, item, tile, n_off, width);
+                const int split = kPair ? 0 : item - tile * p.splits;
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
                 const int per_group = kGroupM * p.tiles_n;
@@ -991,8 +1154,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                         }
                         const uint32_t leader_bar = map_to_rank(smem_u32(full_bar + stage), 0u);
                         tma_load_2d_pair(sa, &tmap_a, leader_bar, kb * kElemsPerRow, tm * kBM);
+                        // this CTA's half of the piece's B rows (a narrow piece uses the first half of the box only)
                         tma_load_2d_pair(sb, &tmap_b, leader_bar, kb * kElemsPerRow,
-                                         tn * kBN + static_cast<int>(pair_rank) * kBRows);
+                                         tn * kBN + n_off + static_cast<int>(pair_rank) * (width / 2));
                     } else {
                         mbar_expect_tx(full_bar + stage, kStageBytes);
                         tma_load_2d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM);
@@ -1014,8 +1178,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             int acc = 0;
             uint32_t acc_phase = 0;
             bool alive = true;
-            for (int item = first_item; alive && item < p.num_tiles * p.splits; item += item_stride) {
-                const int split = item % p.splits;
+            for (int item = first_item; alive && item < p.num_items; item += item_stride) {
+                int tile, n_off, width;
+                decode_item<kPair, kBN>(p, item, tile, n_off, width);
+                const int split = kPair ? 0 : item - tile * p.splits;
+                const uint32_t idesc = (width == kBN) ? p.idesc : p.idesc_narrow;
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
                 if (!mbar_wait(tmem_empty + acc, acc_phase ^ 1u, abort_flag, p.status, 2)) {
@@ -1037,11 +1204,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                         // 32 bytes along k inside the swizzle row = 2 units of the 16-byte address field
                         if (kPair) {
                             umma_pair<kKind>(tmem_d, adesc + static_cast<uint64_t>(2 * ks),
-                                             bdesc + static_cast<uint64_t>(2 * ks), p.idesc,
+                                             bdesc + static_cast<uint64_t>(2 * ks), idesc,
                                              (kb != kb_begin || ks != 0) ? 1u : 0u);
                         } else {
                             umma<kKind>(tmem_d, adesc + static_cast<uint64_t>(2 * ks), bdesc + static_cast<uint64_t>(2 * ks),
-                                        p.idesc, (kb != kb_begin || ks != 0) ? 1u : 0u);
+                                        idesc, (kb != kb_begin || ks != 0) ? 1u : 0u);
                         }
                     }
                     if (kPair) {
@@ -1076,12 +1243,18 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const int part = (warp - 2) / 4;  // warps sharing a quarter split the tile's columns between them
         const EpiParams &e = p.epi;
         float *warp_bias = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + 256) + (warp - 2) * kWarpBiasFloats;
+        // Rows are collected into 128-byte pieces before they are stored only when peers receive copies: for local
+        // memory alone the 16-byte stores straight from registers are faster (measured both ways).
+        unsigned char *warp_stage = e.n_mirrors > 0 ? reinterpret_cast<unsigned char *>(bars) + kTailBytes +
+                                                          (warp - 2) * kWarpStageBytes
+                                                    : nullptr;
         int acc = 0;
         uint32_t acc_phase = 0;
         // "accumulator drained" goes to the MMA thread, which in a pair lives in the leader CTA
         const uint32_t tmem_empty_remote = kPair ? map_to_rank(smem_u32(tmem_empty), 0u) : 0u;
-        for (int item = first_item; item < p.num_tiles * p.splits; item += item_stride) {
-            const int tile = item / p.splits;
+        for (int item = first_item; item < p.num_items; item += item_stride) {
+            int tile, n_off, width;
+            decode_item<kPair, kBN>(p, item, tile, n_off, width);
             const int per_group = kGroupM * p.tiles_n;
             const int group = tile / per_group;
             const int first_m = group * kGroupM;
@@ -1090,9 +1263,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const int tm = kPair ? 2 * (first_m + in_group % gsize) + static_cast<int>(pair_rank) : first_m + in_group % gsize;
             const int tn = in_group / gsize;
             // the warps that share a lane quarter split the tile's 8-column groups between them
-            constexpr int kParts = kEpiWarps / 4, kGroups = kBN / 8;
-            const int g_begin = part * kGroups / kParts, g_end = (part + 1) * kGroups / kParts;
-            const long long n0 = static_cast<long long>(tn) * kBN + g_begin * 8;
+            constexpr int kParts = kEpiWarps / 4;
+            const int piece_groups = width / 8;
+            const int g_begin = part * piece_groups / kParts, g_end = (part + 1) * piece_groups / kParts;
+            const long long n0 = static_cast<long long>(tn) * kBN + n_off + g_begin * 8;
             long long cols = p.n - n0;
             const long long part_cols = static_cast<long long>(g_end - g_begin) * 8;
             cols = cols < 0 ? 0 : (cols < part_cols ? cols : part_cols);
@@ -1143,27 +1317,27 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             }
             switch (e.act) {
                 case KUDNN_B200_ACT_NONE:
-                    epilogue_row<KUDNN_B200_ACT_NONE, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
+                    epilogue_row<KUDNN_B200_ACT_NONE, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     break;
                 case KUDNN_B200_ACT_RELU:
-                    epilogue_row<KUDNN_B200_ACT_RELU, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
+                    epilogue_row<KUDNN_B200_ACT_RELU, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     break;
                 case KUDNN_B200_ACT_SWISH:
                     if (precise) {
-                        epilogue_row<KUDNN_B200_ACT_SWISH, 1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
+                        epilogue_row<KUDNN_B200_ACT_SWISH, 1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     } else {
-                        epilogue_row<KUDNN_B200_ACT_SWISH, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
+                        epilogue_row<KUDNN_B200_ACT_SWISH, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     }
                     break;
                 case KUDNN_B200_ACT_GELU_TANH:
                     if (precise) {
-                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
+                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     } else {
-                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
+                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     }
                     break;
                 default:
-                    epilogue_row<-1, -1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias);
+                    epilogue_row<-1, -1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     break;
             }
             tc_fence_before();
@@ -1401,7 +1575,7 @@ const char *tc_unavailable_reason()
     return g_tc_reason;
 }
 
-cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm_count, TcPlan *plan)
+cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm_count, bool with_staging, TcPlan *plan)
 {
     static_assert(sizeof(CUtensorMap) <= 128, "tensor map storage too small");
     if (!tc_available()) {
@@ -1421,15 +1595,17 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     }
     int pair_clusters = 0;
     if (pair) {
-        const size_t smem = static_cast<size_t>(6) * (kABytes + 128 * kStageRowBytes) + 1024 + kTailBytes;
+        const size_t smem = static_cast<size_t>(with_staging ? 5 : 6) * (kABytes + 128 * kStageRowBytes) + 1024 + kTailBytes +
+                            (with_staging ? kStagingBytes : 0);
         pair_clusters = ops.kind == KUDNN_B200_F32   ? max_pair_clusters<KUDNN_B200_F32>(smem)
                         : ops.kind == KUDNN_B200_F16 ? max_pair_clusters<KUDNN_B200_F16>(smem)
                                                      : max_pair_clusters<KUDNN_B200_BF16>(smem);
         pair = pair_clusters > 0;
     }
     plan->pair = pair ? 1 : 0;
+    plan->narrow_from = 0;
     plan->block_n = bn;
-    plan->stages = (bn == 256 && !pair) ? 4 : 6;
+    plan->stages = ((bn == 256 && !pair) ? 4 : 6) - (with_staging ? 1 : 0);
     // Split-K: with at most half the SMs busy and a long K, the CTAs of a cluster share a tile and cut K between
     // them (2, 4 or 8 ways: the rows of the tile are divided among the ranks for the final pass).  Each split keeps
     // at least four k-blocks so that the pipeline still fills, and no split may be empty.
@@ -1456,10 +1632,19 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     const long long items = tiles * splits;
     plan->grid = splits > 1 ? static_cast<int>(items) : static_cast<int>(tiles < sm_count ? tiles : sm_count);
     const int b_rows = pair ? bn / 2 : bn;  // rows of the weight operand one CTA loads per k-block
-    plan->smem_bytes = static_cast<size_t>(plan->stages) * (kABytes + b_rows * kStageRowBytes) + 1024 + kTailBytes;
+    plan->smem_bytes = static_cast<size_t>(plan->stages) * (kABytes + b_rows * kStageRowBytes) + 1024 + kTailBytes +
+                       (with_staging ? kStagingBytes : 0);
     if (pair) {
         const long long pair_tiles = ((m + 2 * kBM - 1) / (2 * kBM)) * ((n + bn - 1) / bn);
         plan->grid = 2 * static_cast<int>(pair_tiles < pair_clusters ? pair_tiles : pair_clusters);
+        // Tiles left over after the last full wave: if they would keep at most half of the pairs busy, each of them
+        // is processed as two pieces of half the width, which shortens that wave to a little more than half.
+        const long long rem = pair_tiles % pair_clusters;
+        bool narrow = pair_tiles > pair_clusters && rem > 0 && 2 * rem <= pair_clusters;
+        if (const char *env = std::getenv("KUDNN_B200_TC_NARROW_TAIL")) {
+            narrow = narrow && std::atoi(env) != 0;
+        }
+        plan->narrow_from = static_cast<int>(narrow ? pair_tiles - rem : pair_tiles);
     }
     CUtensorMap ta, tb;
     cudaError_t e = encode_kmajor(&ta, ops.a, ops.kind, m, ops.k_total, ops.lda, kBM);
@@ -1492,6 +1677,10 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.status = status;
     p.splits = plan.splits;
     p.kb_per_split = plan.kb_per_split;
+    p.stages = plan.stages;
+    p.num_items = plan.pair ? plan.narrow_from + 2 * (p.num_tiles - plan.narrow_from) : p.num_tiles * plan.splits;
+    p.narrow_from = plan.pair ? plan.narrow_from : p.num_tiles;
+    p.idesc_narrow = make_idesc(ops.kind, plan.block_n / 2, plan.pair ? 2 * kBM : kBM);
     if (plan.pair) {
         switch (ops.kind) {
             case KUDNN_B200_F32:

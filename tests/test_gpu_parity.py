@@ -213,6 +213,16 @@ def test_tc_split_k(cuda_device, monkeypatch, dtype, splits, m, n, k):
     assert np.array_equal(first[0], second[0]) and np.array_equal(first[1], second[1])
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("m,n,k", [(2560, 2048, 136), (2400, 2300, 64), (512, 9000, 128)])
+def test_tc_cta_pairs(cuda_device, dtype, m, n, k):
+    """Large problems run on clusters of two CTAs (256 x 256 tiles); the first two shapes leave a short last wave,
+    whose tiles are then cut into two pieces of half the width.  Ragged edges in m and n included."""
+    case = dict(m=m, n=n, k=k, dtype=dtype, bias="row", act=kb.ACT_GELU_TANH, res_op=kb.RES_IDENTICAL, x_dist="normal",
+                w_std=0.05, seed=49)
+    helpers.parity(case, cuda_device, kernel=kb.KERNEL_TC, acc=ko.ACC_F64, expect_kernel=kb.KERNEL_TC)
+
+
 def test_tc_agrees_with_general_kernel(cuda_device):
     case = dict(m=512, n=768, k=512, dtype="bf16", bias="row", act=kb.ACT_SWISH, x_dist="normal", w_std=0.03, seed=47)
     desc, arrays, c = helpers.build_case(case)

@@ -61,7 +61,7 @@ constexpr int kEpiWarps = 12;                      // two per scheduler: each hi
 constexpr int kTcThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA, the rest: epilogue
 constexpr int kStageRowBytes = 128;  // one swizzle row: 64 16-bit or 32 32-bit elements
 constexpr int kABytes = kBM * kStageRowBytes;
-constexpr int kGroupM = 16;  // tile rows per raster group
+constexpr int kMaxGroupM = 16;  // most tile rows per raster group
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about two seconds at 2 GHz
 constexpr int kWarpBiasFloats = 128;  // per epilogue warp: the bias values of its columns of the current tile, as fp32
 constexpr int kWarpStageBytes = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes of output on their way to memory
@@ -81,6 +81,7 @@ struct TcParams {
     // each contracts over kb_per_split k-blocks, and the partial tiles are added through distributed shared memory
     int splits, kb_per_split;
     int stages;  // depth of the shared-memory ring
+    int group_m;  // tile rows per raster group: consecutive work items walk down group_m tile rows, then one tile right
     // CTA pairs: work items [0, narrow_from) are whole 256 x BN tiles; each later tile is two items of half the width,
     // so that a last wave that would keep fewer than half the pairs busy is spread over twice as many
     int num_items, narrow_from;
@@ -1131,10 +1132,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 const int split = kPair ? 0 : item - tile * p.splits;
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
-                const int per_group = kGroupM * p.tiles_n;
+                const int per_group = p.group_m * p.tiles_n;
                 const int group = tile / per_group;
-                const int first_m = group * kGroupM;
-                const int gsize = (p.tiles_m - first_m < kGroupM) ? (p.tiles_m - first_m) : kGroupM;
+                const int first_m = group * p.group_m;
+                const int gsize = (p.tiles_m - first_m < p.group_m) ? (p.tiles_m - first_m) : p.group_m;
                 const int in_group = tile - group * per_group;
                 const int tn = in_group / gsize;
                 // row of 128-row blocks this CTA loads: the pair's tile is 256 rows tall
@@ -1255,10 +1256,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         for (int item = first_item; item < p.num_items; item += item_stride) {
             int tile, n_off, width;
             decode_item<kPair, kBN>(p, item, tile, n_off, width);
-            const int per_group = kGroupM * p.tiles_n;
+            const int per_group = p.group_m * p.tiles_n;
             const int group = tile / per_group;
-            const int first_m = group * kGroupM;
-            const int gsize = (p.tiles_m - first_m < kGroupM) ? (p.tiles_m - first_m) : kGroupM;
+            const int first_m = group * p.group_m;
+            const int gsize = (p.tiles_m - first_m < p.group_m) ? (p.tiles_m - first_m) : p.group_m;
             const int in_group = tile - group * per_group;
             const int tm = kPair ? 2 * (first_m + in_group % gsize) + static_cast<int>(pair_rank) : first_m + in_group % gsize;
             const int tn = in_group / gsize;
@@ -1371,10 +1372,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
         if (warp >= 2 && *abort_flag == 0) {
             const int tile = static_cast<int>(blockIdx.x) / p.splits;
-            const int per_group = kGroupM * p.tiles_n;
+            const int per_group = p.group_m * p.tiles_n;
             const int group = tile / per_group;
-            const int first_m = group * kGroupM;
-            const int gsize = (p.tiles_m - first_m < kGroupM) ? (p.tiles_m - first_m) : kGroupM;
+            const int first_m = group * p.group_m;
+            const int gsize = (p.tiles_m - first_m < p.group_m) ? (p.tiles_m - first_m) : p.group_m;
             const int in_group = tile - group * per_group;
             const int tm = first_m + in_group % gsize;
             const int tn = in_group / gsize;
@@ -1678,6 +1679,20 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.splits = plan.splits;
     p.kb_per_split = plan.kb_per_split;
     p.stages = plan.stages;
+    {
+        // The A rows of one raster group are re-read for every tile column and should stay in L2 next to the
+        // streaming weights: at most about 32 MB of them (config 2: 16 rows of 256 x 4096 bf16; K = 8192: 8 rows).
+        const long long tile_bytes = static_cast<long long>(tile_rows) * ops.k_total * dtype_size(ops.kind);
+        long long gm = (32ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
+        gm = gm < 2 ? 2 : (gm > kMaxGroupM ? kMaxGroupM : gm);
+        if (const char *env = std::getenv("KUDNN_B200_TC_GROUP_M")) {
+            const int v = std::atoi(env);
+            if (v >= 1 && v <= 64) {
+                gm = v;
+            }
+        }
+        p.group_m = static_cast<int>(gm);
+    }
     p.num_items = plan.pair ? plan.narrow_from + 2 * (p.num_tiles - plan.narrow_from) : p.num_tiles * plan.splits;
     p.narrow_from = plan.pair ? plan.narrow_from : p.num_tiles;
     p.idesc_narrow = make_idesc(ops.kind, plan.block_n / 2, plan.pair ? 2 * kBM : kBM);

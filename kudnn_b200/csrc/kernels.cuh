@@ -30,6 +30,7 @@ struct GemvPlan {
     int grid, block;    // launch shape
     int shape;          // index of the compiled (threads, CTAs per SM) variant
     int ksplit;         // K chunks (MMA kernel)
+    int wide;           // MMA kernel with fragment-shaped loads: 1 = blocks of 64 k, 32 bytes per lane
     int active_warps;   // warps that take a span of the flattened work
     long long span;     // work blocks per active warp
     int slots;          // partial slots per row / row group

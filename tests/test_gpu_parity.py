@@ -85,23 +85,33 @@ def test_gemv_fma(cuda_device, dtype, m):
     helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_FMA, expect_kernel=kb.KERNEL_GEMV_FMA)
 
 
-@pytest.mark.parametrize("staged", ["1", "0"])
+@pytest.mark.parametrize("staged,wide", [("1", "1"), ("0", "1"), ("0", "0")])
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 @pytest.mark.parametrize("m", [1, 3, 4, 7, 8, 9, 16])
-def test_gemv_mma(cuda_device, monkeypatch, staged, dtype, m):
+def test_gemv_mma(cuda_device, monkeypatch, staged, wide, dtype, m):
     monkeypatch.setenv("KUDNN_B200_GEMV_STAGED", staged)  # weight feed: through per-warp staging, or fragment-shaped loads
+    monkeypatch.setenv("KUDNN_B200_GEMV_WIDE", wide)      # fragment-shaped loads of 32 or 16 bytes per lane (m > 8)
     case = dict(m=m, n=1003, k=1048, dtype=dtype, res_op=kb.RES_ELTWISE_MUL, x_dist="normal", w_std=0.05, seed=32)
     helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_MMA, expect_kernel=kb.KERNEL_GEMV_MMA)
 
 
-@pytest.mark.parametrize("staged", ["1", "0"])
+@pytest.mark.parametrize("staged,wide", [("1", "1"), ("0", "1"), ("0", "0")])
 @pytest.mark.parametrize("kernel", [kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA])
 @pytest.mark.parametrize("n,k", [(8, 8), (5, 4096), (40000, 64), (777, 2504), (2600, 16384), (300, 8192)])
-def test_gemv_shapes_that_cut_units(cuda_device, monkeypatch, staged, kernel, n, k):
+def test_gemv_shapes_that_cut_units(cuda_device, monkeypatch, staged, wide, kernel, n, k):
     monkeypatch.setenv("KUDNN_B200_GEMV_STAGED", staged)
+    monkeypatch.setenv("KUDNN_B200_GEMV_WIDE", wide)
     # tiny, one long row, many short rows, odd sizes: exercise whole units, split units and idle warps
     case = dict(m=2, n=n, k=k, dtype="bf16", bias="row", x_dist="normal", w_std=0.05, seed=33)
     helpers.parity(case, cuda_device, kernel=kernel, expect_kernel=kernel)
+
+
+@pytest.mark.parametrize("wide", ["1", "0"])
+@pytest.mark.parametrize("n,k", [(8, 8), (5, 4096), (4000, 72), (777, 2504), (2600, 16384)])
+def test_gemv_mma_sixteen_rows_shapes(cuda_device, monkeypatch, wide, n, k):
+    monkeypatch.setenv("KUDNN_B200_GEMV_WIDE", wide)
+    case = dict(m=12, n=n, k=k, dtype="bf16", bias="row", act=kb.ACT_SWISH, x_dist="normal", w_std=0.05, seed=37)
+    helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_MMA, expect_kernel=kb.KERNEL_GEMV_MMA)
 
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])

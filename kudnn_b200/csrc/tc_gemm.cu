@@ -590,11 +590,13 @@ __device__ __forceinline__ void round_rne8(float (&v)[8])
 // Arithmetic of the fast form of epilogue_group8 (beta == 0, side inputs contiguous along the row and 16-byte
 // aligned at this group, all 8 columns in range), first half: v receives the 8 values of c, exactly representable
 // in c's type.
-template <int kAct, int kPrecise>
+// kDt: element type of c, bias, res and out when they all equal the kernel's input type (the common case: every
+// type test below is then decided at compile time), or -1 when the types are read from the descriptor.
+template <int kAct, int kDt>
 __device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32_t (&raw)[8], const RowPointers &rp,
                                                 int byte_off_bias, int g, float (&v)[8])
 {
-    const int ct = e.c_dtype;
+    const int ct = kDt > 0 ? kDt : e.c_dtype;
     float side[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -612,7 +614,7 @@ __device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32
         side[0] = b0.x; side[1] = b0.y; side[2] = b0.z; side[3] = b0.w;
         side[4] = b1.x; side[5] = b1.y; side[6] = b1.z; side[7] = b1.w;
     } else if (rp.bias_mode == 1) {
-        load8_vec(rp.bias + byte_off_bias, e.bias_dtype, side);
+        load8_vec(rp.bias + byte_off_bias, kDt > 0 ? kDt : e.bias_dtype, side);
     } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -649,7 +651,7 @@ __device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32
         } else {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                v[j] = activation<kPrecise == 1>(v[j], kAct, e.act_alpha);
+                v[j] = activation<kDt == KUDNN_B200_F32>(v[j], kAct, e.act_alpha);
             }
         }
         if (ct == KUDNN_B200_F16) {
@@ -664,10 +666,11 @@ __device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32
 }
 
 // Second half: v holds the values of c and is replaced by those of the second output (c (+) res).
+template <int kDt>
 __device__ __forceinline__ void compute_out8_fast(const EpiParams &e, const RowPointers &rp, int byte_off_res, float (&v)[8])
 {
     float side[8];
-    load8_vec(rp.res + byte_off_res, e.res_dtype, side);
+    load8_vec(rp.res + byte_off_res, kDt > 0 ? kDt : e.res_dtype, side);
     if (e.res_op == KUDNN_B200_RES_IDENTICAL) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -684,7 +687,7 @@ __device__ __forceinline__ void compute_out8_fast(const EpiParams &e, const RowP
             v[j] *= side[j];
         }
     }
-    const int ot = e.out_dtype;
+    const int ot = kDt > 0 ? kDt : e.out_dtype;
     if (ot == KUDNN_B200_F16) {
         round_rne8<KUDNN_B200_F16>(v);
     } else if (ot == KUDNN_B200_BF16) {
@@ -694,24 +697,24 @@ __device__ __forceinline__ void compute_out8_fast(const EpiParams &e, const RowP
 
 // Fast form of epilogue_group8: same arithmetic, no address arithmetic beyond pointer bumps, one 16-byte (fp32: two)
 // store per tensor and mirror.
-template <int kAct, int kPrecise>
+template <int kAct, int kDt>
 __device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const uint32_t (&raw)[8], const RowPointers &rp,
                                                      int byte_off_c, int byte_off_bias, int byte_off_res, int byte_off_out,
                                                      int g)
 {
     float v[8];
-    compute_c8_fast<kAct, kPrecise>(e, raw, rp, byte_off_bias, g, v);
+    compute_c8_fast<kAct, kDt>(e, raw, rp, byte_off_bias, g, v);
     if (rp.c != nullptr) {
-        store8_vec(rp.c + byte_off_c, e.c_dtype, v);
+        store8_vec(rp.c + byte_off_c, kDt > 0 ? kDt : e.c_dtype, v);
         for (int i = 0; i < e.n_mirrors; ++i) {
-            store8_vec(rp.c + e.c_delta[i] + byte_off_c, e.c_dtype, v);
+            store8_vec(rp.c + e.c_delta[i] + byte_off_c, kDt > 0 ? kDt : e.c_dtype, v);
         }
     }
     if (e.res_op != KUDNN_B200_RES_NONE) {
-        compute_out8_fast(e, rp, byte_off_res, v);
-        store8_vec(rp.out + byte_off_out, e.out_dtype, v);
+        compute_out8_fast<kDt>(e, rp, byte_off_res, v);
+        store8_vec(rp.out + byte_off_out, kDt > 0 ? kDt : e.out_dtype, v);
         for (int i = 0; i < e.n_mirrors; ++i) {
-            store8_vec(rp.out + e.out_delta[i] + byte_off_out, e.out_dtype, v);
+            store8_vec(rp.out + e.out_delta[i] + byte_off_out, kDt > 0 ? kDt : e.out_dtype, v);
         }
     }
 }
@@ -756,19 +759,19 @@ __device__ __forceinline__ void pack8_to_chunks(const float (&v)[8], int dtype, 
     }
 }
 
-template <int kAct, int kPrecise>
+template <int kAct, int kDt>
 __device__ __noinline__ void epilogue_rows_coalesced(const EpiParams &e, uint32_t taddr, int groups, const RowPointers rp,
                                                         unsigned char *stage, int lane)
 {
     // the one output tensor that is written: c, or the second output when c is not requested
     const bool second = rp.c == nullptr;
-    const int odt = second ? e.out_dtype : e.c_dtype;
+    const int odt = kDt > 0 ? kDt : (second ? e.out_dtype : e.c_dtype);
     const int chunks_per_group = (odt == KUDNN_B200_F32) ? 2 : 1;
     const int groups_per_pass = 8 / chunks_per_group;
     const long long pitch = (second ? e.out_sm : e.c_sm) * dtype_size(odt);  // bytes between rows
     char *row0 = (second ? rp.out : rp.c) - static_cast<long long>(lane) * pitch;  // row of lane 0
     const long long *delta = second ? e.out_delta : e.c_delta;
-    const int step_bias = 8 * dtype_size(e.bias_dtype), step_res = 8 * dtype_size(e.res_dtype);
+    const int step_bias = 8 * dtype_size(kDt > 0 ? kDt : e.bias_dtype), step_res = 8 * dtype_size(kDt > 0 ? kDt : e.res_dtype);
     const uint32_t stage_addr = smem_u32(stage);
     const uint32_t my_row = stage_addr + static_cast<uint32_t>(lane * 128);
 
@@ -788,9 +791,9 @@ __device__ __noinline__ void epilogue_rows_coalesced(const EpiParams &e, uint32_
                 tmem_load_8_issue(taddr + static_cast<uint32_t>((g + 1) * 8), next);
             }
             float v[8];
-            compute_c8_fast<kAct, kPrecise>(e, cur, rp, g * step_bias, g, v);
+            compute_c8_fast<kAct, kDt>(e, cur, rp, g * step_bias, g, v);
             if (second) {
-                compute_out8_fast(e, rp, g * step_res, v);
+                compute_out8_fast<kDt>(e, rp, g * step_res, v);
             }
             uint4 lo, hi;
             pack8_to_chunks(v, odt, lo, hi);
@@ -872,7 +875,7 @@ __device__ __forceinline__ bool setup_row_pointers(const EpiParams &e, bool row_
     return fast;
 }
 
-template <int kAct, int kPrecise>
+template <int kAct, int kDt>
 __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr, bool row_ok, long long mi, long long n0,
                                              int groups, const float *staged_bias, unsigned char *stage, int lane)
 {
@@ -888,11 +891,11 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
     // all 32 rows on the vector path and a single output tensor: collect 128-byte row pieces and store those
     const bool one_output = (rp.c != nullptr) != (e.res_op != KUDNN_B200_RES_NONE);
     if (stage != nullptr && __all_sync(0xffffffffu, fast && one_output)) {
-        epilogue_rows_coalesced<kAct, kPrecise>(e, taddr, groups, rp, stage, lane);
+        epilogue_rows_coalesced<kAct, kDt>(e, taddr, groups, rp, stage, lane);
         return;
     }
-    const int step_c = 8 * dtype_size(e.c_dtype), step_bias = 8 * dtype_size(e.bias_dtype);
-    const int step_res = 8 * dtype_size(e.res_dtype), step_out = 8 * dtype_size(e.out_dtype);
+    const int step_c = 8 * dtype_size(kDt > 0 ? kDt : e.c_dtype), step_bias = 8 * dtype_size(kDt > 0 ? kDt : e.bias_dtype);
+    const int step_res = 8 * dtype_size(kDt > 0 ? kDt : e.res_dtype), step_out = 8 * dtype_size(kDt > 0 ? kDt : e.out_dtype);
 
     uint32_t next[8], cur[8];
     tmem_load_8_issue(taddr, next);
@@ -908,9 +911,9 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
             tmem_load_8_issue(taddr + static_cast<uint32_t>((g + 1) * 8), next);
         }
         if (fast) {
-            epilogue_group8_fast<kAct, kPrecise>(e, cur, rp, g * step_c, g * step_bias, g * step_res, g * step_out, g);
+            epilogue_group8_fast<kAct, kDt>(e, cur, rp, g * step_c, g * step_bias, g * step_res, g * step_out, g);
         } else if (row_ok) {
-            epilogue_group8<kAct, kPrecise>(e, cur, mi, n0 + g * 8);
+            epilogue_group8<kAct, (kDt < 0 ? -1 : (kDt == KUDNN_B200_F32 ? 1 : 0))>(e, cur, mi, n0 + g * 8);
         }
     }
 }
@@ -975,7 +978,7 @@ __device__ __forceinline__ void dump_partial_row(uint32_t taddr, float *dst, int
 }
 
 // The epilogue threads of cluster rank `rank` finish rows [rank * 128 / splits, (rank + 1) * 128 / splits) of the tile.
-template <int kAct, int kPrecise, int kBN>
+template <int kAct, int kDt, int kBN>
 __device__ __forceinline__ void finish_split_rows(const EpiParams &e, const float *part, int splits, uint32_t rank, int tm,
                                                   int tn, int m, int n, int epi_tid)
 {
@@ -1015,9 +1018,9 @@ __device__ __forceinline__ void finish_split_rows(const EpiParams &e, const floa
         }
         RowPointers rp;
         if (setup_row_pointers(e, true, mi, ni, 1, rp)) {
-            epilogue_group8_fast<kAct, kPrecise>(e, raw, rp, 0, 0, 0, 0, 0);
+            epilogue_group8_fast<kAct, kDt>(e, raw, rp, 0, 0, 0, 0, 0);
         } else {
-            epilogue_group8<kAct, kPrecise>(e, raw, mi, ni);
+            epilogue_group8<kAct, (kDt < 0 ? -1 : (kDt == KUDNN_B200_F32 ? 1 : 0))>(e, raw, mi, ni);
         }
     }
 }
@@ -1297,7 +1300,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                        static_cast<uint32_t>(acc * kBN);
             const uint32_t taddr_part = taddr_row + static_cast<uint32_t>(g_begin * 8);
-            const bool precise = e.c_dtype == KUDNN_B200_F32;
             if (p.splits > 1) {
                 // partial tile -> this CTA's shared memory (the stage buffers: every load into them has landed and
                 // every MMA that read them has completed once the accumulator barrier has fired); it is added to
@@ -1316,26 +1318,24 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 }
                 break;  // one work item per CTA in this mode
             }
-            switch (e.act) {
+            // All output-side tensors in the kernel's input type (the usual case): the epilogue variants with the
+            // element type fixed at compile time.  Any other mix, or a rarer activation: the variant that reads the
+            // types and the activation from the descriptor.
+            const bool typed = e.c_dtype == kKind && (e.has_bias == 0 || e.bias_dtype == kKind) &&
+                               (e.res_op == KUDNN_B200_RES_NONE || (e.res_dtype == kKind && e.out_dtype == kKind));
+            const int act_case = typed ? e.act : -1;
+            switch (act_case) {
                 case KUDNN_B200_ACT_NONE:
-                    epilogue_row<KUDNN_B200_ACT_NONE, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
+                    epilogue_row<KUDNN_B200_ACT_NONE, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     break;
                 case KUDNN_B200_ACT_RELU:
-                    epilogue_row<KUDNN_B200_ACT_RELU, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
+                    epilogue_row<KUDNN_B200_ACT_RELU, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     break;
                 case KUDNN_B200_ACT_SWISH:
-                    if (precise) {
-                        epilogue_row<KUDNN_B200_ACT_SWISH, 1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    } else {
-                        epilogue_row<KUDNN_B200_ACT_SWISH, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    }
+                    epilogue_row<KUDNN_B200_ACT_SWISH, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     break;
                 case KUDNN_B200_ACT_GELU_TANH:
-                    if (precise) {
-                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    } else {
-                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, 0>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    }
+                    epilogue_row<KUDNN_B200_ACT_GELU_TANH, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
                     break;
                 default:
                     epilogue_row<-1, -1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
@@ -1383,27 +1383,20 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const EpiParams &e = p.epi;
             const uint32_t rank = cluster_rank();
             const int epi_tid = static_cast<int>(threadIdx.x) - 64;
-            const bool precise = e.c_dtype == KUDNN_B200_F32;
-            switch (e.act) {
+            const bool typed = e.c_dtype == kKind && (e.has_bias == 0 || e.bias_dtype == kKind) &&
+                               (e.res_op == KUDNN_B200_RES_NONE || (e.res_dtype == kKind && e.out_dtype == kKind));
+            switch (typed ? e.act : -1) {
                 case KUDNN_B200_ACT_NONE:
-                    finish_split_rows<KUDNN_B200_ACT_NONE, 0, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    finish_split_rows<KUDNN_B200_ACT_NONE, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
                     break;
                 case KUDNN_B200_ACT_RELU:
-                    finish_split_rows<KUDNN_B200_ACT_RELU, 0, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                    finish_split_rows<KUDNN_B200_ACT_RELU, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
                     break;
                 case KUDNN_B200_ACT_SWISH:
-                    if (precise) {
-                        finish_split_rows<KUDNN_B200_ACT_SWISH, 1, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    } else {
-                        finish_split_rows<KUDNN_B200_ACT_SWISH, 0, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    }
+                    finish_split_rows<KUDNN_B200_ACT_SWISH, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
                     break;
                 case KUDNN_B200_ACT_GELU_TANH:
-                    if (precise) {
-                        finish_split_rows<KUDNN_B200_ACT_GELU_TANH, 1, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    } else {
-                        finish_split_rows<KUDNN_B200_ACT_GELU_TANH, 0, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    }
+                    finish_split_rows<KUDNN_B200_ACT_GELU_TANH, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
                     break;
                 default:
                     finish_split_rows<-1, -1, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);

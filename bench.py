@@ -506,9 +506,26 @@ def main():
         except Exception as exc:  # the oracle is optional test infrastructure
             line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port",
                                     "sample": "unavailable: %s" % exc}
+    elif world > 1 and not args.no_extras and wname != "c5n":
+        # every rank pushes its own rows through the host-pointer call at the same time (they share the host's PCIe
+        # and memory system); the job's rate is all rows over the slowest rank's time
+        e = e2e_leg(torch, kb, w, wname, m_local, device, min(args.steps, 10), sync=dist.barrier)
+        tmax = torch.tensor([e["ms_per_step"]], device=device, dtype=torch.float64)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        worst_ms = float(tmax.item())
+        if wname == "c4":
+            e["value"] = algorithmic_bytes(w, m_local) * world / (worst_ms * 1e-3) / 1e9
+        else:
+            e["value"] = job_flops / (worst_ms * 1e-3) / 1e12
+        e["ms_per_step"] = worst_ms
+        e["h2d_bytes_per_step"] *= world
+        e["d2h_bytes_per_step"] *= world
+        e["timing"] = "host clock around run_host calls on every rank at once; slowest rank; bytes summed over ranks"
+        line["e2e"] = e
     elif world > 1:
         line["e2e"] = {"value": None, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                       "note": "measured at n_gpus=1 only"}
+                       "note": "not measured in this mode (--no-extras, or the column-sharded workload whose output "
+                               "lives in peer-mapped device buffers)"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -517,7 +534,7 @@ def main():
     return 0
 
 
-def e2e_leg(torch, kb, w, wname, m, device, steps):
+def e2e_leg(torch, kb, w, wname, m, device, steps, sync=None):
     """The same step through kudnn_b200_linear_run_host: pinned host buffers in, pinned host buffers out."""
     tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[w["dtype"]]
     x, wt, bias, res = make_inputs(w, m, torch.device("cpu"), seed=0)
@@ -538,6 +555,8 @@ def e2e_leg(torch, kb, w, wname, m, device, steps):
     for _ in range(3):
         step()
     torch.cuda.synchronize()
+    if sync is not None:
+        sync()
     t0 = time.perf_counter()
     for _ in range(steps):
         step()  # returns after the device-to-host copy has completed

@@ -41,13 +41,14 @@ WORKLOADS = {
                label="Linear+SiLU bf16 M32768 K8192 N28672"),
 }
 
-# DRAM bytes per launch of the dominant kernel, from the ncu captures summarised under profiles/ (null until captured)
+# DRAM bytes per launch of the dominant kernel, from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum) of
+# reduced cases, scaled to the full launch by the rows processed (null where nothing was captured)
 NCU_TRAFFIC_BYTES = {
-    # profiles/tc_linear_bf16_silu_m2048_n11008_k4096.md: 110.7 MB read + 29.1 MB written at m=2048; x and y scale with
-    # the rows, W does not, and the part of y still in L2 at kernel end is counted as written
+    # ncu capture of a half-size case (m = 2048): 110.7 MB read + 29.1 MB written; x and y scale with the rows, W does
+    # not, and the part of y still in L2 at kernel end is counted as written
     "c2": 127.5e6 + 90.2e6,
-    # profiles/gemv_decode_bf16_n8192_k8192.md: traffic equals the algorithmic bytes within 0.1 % (+3 % for the m=16
-    # partial sums); scaled to n=28672 by the rows
+    # ncu capture of an n = 8192 case: traffic equals the algorithmic bytes within 0.1 % (+3 % for the m = 16 partial
+    # sums); scaled to n = 28672 by the rows
     "c4": 471.9e6 + 11.5e6,
 }
 

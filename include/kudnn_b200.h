@@ -64,7 +64,6 @@ extern "C" {
 #define KUDNN_B200_KERNEL_GEMV_FMA 2 /* m <= 4 streaming kernel, fp32 FMA + warp-shuffle reduction */
 #define KUDNN_B200_KERNEL_GEMV_MMA 3 /* m <= 16 streaming kernel, 16-bit inputs */
 #define KUDNN_B200_KERNEL_TC 4       /* tcgen05 / TMEM tensor-core kernel fed by TMA */
-#define KUDNN_B200_KERNEL_GEMV_RING 5 /* m <= 16 streaming kernel, weights through a bulk-copy shared-memory ring */
 
 /* Replaces the argument lists of the reference constructors:
  *   Gemm(aInfo,bInfo,cInfo,biasInfo,numThreads)                     src/dnn/include/operations/kudnn_gemm.hpp:36-39
@@ -112,18 +111,30 @@ KUDNN_B200_API int kudnn_b200_linear_destroy(kudnn_b200_linear_t handle);
 
 /* Pre-packs the weight operand `b` (host or device memory) into the layout the chosen kernel streams (K-major,
  * 16-byte aligned rows; fp32 weights additionally split into TF32 hi/lo planes).  Later runs whose args->b equals
- * `b` use the packed copy and do not read `b` again.  Replaces the per-call packing inside the reference's BLAS/JIT
+ * `b` use the packed copy and do not read `b` again: the packed copy is recognised by the ADDRESS alone.  After the
+ * weights at that address have changed (an in-place update, or a new tensor the allocator placed where the old one
+ * was) call prepack again, or kudnn_b200_linear_unpack to go back to reading `b` on every run; otherwise runs keep
+ * using the old values.  Replaces the per-call packing inside the reference's BLAS/JIT
  * (src/dnn/src/matmul_jit/MatrixComputation/kudnn_default_impl_fp16fp16f32f32.cpp:929-962). */
 KUDNN_B200_API int kudnn_b200_linear_prepack(kudnn_b200_linear_t handle, const void *b, void *cuda_stream);
+/* Forgets (and frees) the packed copy.  No counterpart in the reference, which packs on every call. */
+KUDNN_B200_API int kudnn_b200_linear_unpack(kudnn_b200_linear_t handle);
 
 /* Execute with DEVICE pointers on `cuda_stream` (a cudaStream_t, NULL = default stream); asynchronous.
+ * A handle owns device scratch (split-K partial sums and arrival counters, packed activations, the status block)
+ * that all of its runs share: the handle's lock serialises the host side only, so runs of ONE handle must not overlap
+ * on the GPU.  Keep a handle on one stream at a time; kudnn_b200_linear_clone gives every further stream a handle of
+ * its own.
  * Replaces GemmImpl::Run / LinearActivationLayerFWDImpl::Run / LinearResFWDImpl::Run
  * (src/dnn/src/kudnn_gemm.cpp:859-877, kudnn_linear_activationlayer.cpp:40-56, kudnn_linear_res.cpp:184-202). */
 KUDNN_B200_API int kudnn_b200_linear_run(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args,
                                          void *cuda_stream);
 
 /* Execute with HOST pointers, as the reference's callers pass them: stages inputs to the device, runs, copies the
- * outputs back and synchronises.  A weight pointer that was pre-packed is not copied again. */
+ * outputs back and synchronises.  A weight pointer that was pre-packed is not copied again.  Large 2-D problems
+ * (m >= 1024) whose a and output buffers are page-locked (cudaHostAlloc / cudaHostRegister) are cut into blocks of
+ * rows so that copy-in, kernel and copy-out overlap; pageable buffers take the single-shot path (copy everything in,
+ * one run, copy everything out), because their copies hold the host and could not overlap anyway. */
 KUDNN_B200_API int kudnn_b200_linear_run_host(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args);
 
 /* Looks at where args->a lives and calls kudnn_b200_linear_run (device memory) or kudnn_b200_linear_run_host (anything
@@ -137,11 +148,17 @@ KUDNN_B200_API int kudnn_b200_linear_run_any(kudnn_b200_linear_t handle, const k
  * plug-ins whose host forbids allocation inside an operator call, decode loops that cannot risk the device
  * synchronisation an allocation may cause.  This entry point has no counterpart in the reference.  It takes the
  * descriptor directly (no handle) and device pointers; the split-K scratch of the streaming kernels is a fixed
- * 8 MiB (+ 64 KiB of counters) array inside the library's device image, held by every GPU that loads the library
- * until the process exits.  Problems whose scratch does not fit return KUDNN_B200_UNSUPPORTED and launch nothing.
+ * 8 MiB (+ 64 KiB of counters) array inside the library's device image, held by every GPU on which the library's
+ * device code has been loaded, until the process exits.  Problems whose scratch does not fit return
+ * KUDNN_B200_UNSUPPORTED and launch nothing.
  * All calls on a device share that array: calls that overlap on the GPU race and give undefined results, so keep
- * them on one stream.  The first call on each device resolves the array's device address; make that call before
- * beginning any stream capture. */
+ * them on one stream.
+ * Warm-up rule.  The CUDA runtime loads device code lazily (CUDA_MODULE_LOADING=LAZY is the default since 12.2): the
+ * array comes into existence when the first call on a device resolves its address, and each kernel variant (element
+ * type x row-count class m = 1 / 2..8 / 9..16) is loaded by the first call that launches it.  Both take device
+ * memory from the driver, once.  So make one call per device and per variant you will use BEFORE handing the rest
+ * of HBM to your pools and before any stream capture (or run with CUDA_MODULE_LOADING=EAGER); from then on a call
+ * takes no device memory at all. */
 KUDNN_B200_API int kudnn_b200_linear_run_static_scratch(const kudnn_b200_linear_desc *desc,
                                                         const kudnn_b200_linear_args *args, void *cuda_stream);
 
@@ -166,6 +183,15 @@ KUDNN_B200_API int kudnn_b200_peer_buffer_create(size_t bytes, void **dev_ptr, u
 KUDNN_B200_API int kudnn_b200_peer_buffer_open(const unsigned char *handle, void **dev_ptr);
 KUDNN_B200_API int kudnn_b200_peer_buffer_close(void *dev_ptr);
 KUDNN_B200_API int kudnn_b200_peer_buffer_destroy(void *dev_ptr);
+
+/* Test hooks (no counterpart in the reference).  set_wait: device-side waits of this handle's tensor-core launches
+ * give up after `wait_limit_cycles` SM cycles (0 = the default, about two seconds), and the producer of CTA 0 leaves
+ * out the loads of k-block `skip_kblock` of its first tile (-1 = never), so that one bounded wait runs out, the
+ * kernel drains, frees its tensor memory and the run reports KUDNN_B200_TIMEOUT; nothing faults or hangs.
+ * fail_allocation: the nth (0 = next) device allocation the library attempts fails as if the device were out of
+ * memory (KUDNN_B200_ALLOC_FAILED); negative = off. */
+KUDNN_B200_API int kudnn_b200_debug_set_wait(kudnn_b200_linear_t handle, long long wait_limit_cycles, int skip_kblock);
+KUDNN_B200_API int kudnn_b200_debug_fail_allocation(int nth);
 
 /* Introspection used by tests and the benchmark. */
 KUDNN_B200_API int kudnn_b200_linear_force_kernel(kudnn_b200_linear_t handle, int kernel);

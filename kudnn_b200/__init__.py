@@ -8,17 +8,17 @@ sm_100 device is present, calls fail with an error.
 from .capi import (  # noqa: F401
     ACT_GELU_ERF, ACT_GELU_TANH, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH,
     BF16, F16, F32,
-    KERNEL_AUTO, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_GEMV_RING, KERNEL_SIMT, KERNEL_TC, KERNEL_NAMES,
+    KERNEL_AUTO, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_SIMT, KERNEL_TC, KERNEL_NAMES,
     RES_ELTWISE_MUL, RES_EXT, RES_IDENTICAL, RES_NONE,
-    KudnnError, Linear, LinearDesc, library, library_path, make_desc, run_static_scratch, shard_range,
+    KudnnError, Linear, LinearDesc, debug_fail_allocation, library, library_path, make_desc, run_static_scratch, shard_range,
     peer_buffer_close, peer_buffer_create, peer_buffer_destroy, peer_buffer_open,
 )
 
 __all__ = [
     "ACT_GELU_ERF", "ACT_GELU_TANH", "ACT_NONE", "ACT_RELU", "ACT_SIGMOID", "ACT_SWISH", "ACT_TANH",
     "BF16", "F16", "F32",
-    "KERNEL_AUTO", "KERNEL_GEMV_FMA", "KERNEL_GEMV_MMA", "KERNEL_GEMV_RING", "KERNEL_SIMT", "KERNEL_TC", "KERNEL_NAMES",
+    "KERNEL_AUTO", "KERNEL_GEMV_FMA", "KERNEL_GEMV_MMA", "KERNEL_SIMT", "KERNEL_TC", "KERNEL_NAMES",
     "RES_ELTWISE_MUL", "RES_EXT", "RES_IDENTICAL", "RES_NONE",
-    "KudnnError", "Linear", "LinearDesc", "library", "library_path", "make_desc", "run_static_scratch", "shard_range",
+    "KudnnError", "Linear", "LinearDesc", "debug_fail_allocation", "library", "library_path", "make_desc", "run_static_scratch", "shard_range",
     "peer_buffer_close", "peer_buffer_create", "peer_buffer_destroy", "peer_buffer_open",
 ]

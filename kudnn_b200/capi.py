@@ -9,8 +9,8 @@ import os
 F32, F16, BF16 = 1, 2, 3
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_SIGMOID, ACT_GELU_TANH, ACT_SWISH, ACT_GELU_ERF = 0, 5, 9, 10, 20, 25, 27
 RES_NONE, RES_EXT, RES_IDENTICAL, RES_ELTWISE_MUL = 0, 1, 2, 3
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_TC, KERNEL_GEMV_RING = 0, 1, 2, 3, 4, 5
-KERNEL_NAMES = {0: "auto", 1: "simt", 2: "gemv_fma", 3: "gemv_mma", 4: "tc", 5: "gemv_ring"}
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_TC = 0, 1, 2, 3, 4
+KERNEL_NAMES = {0: "auto", 1: "simt", 2: "gemv_fma", 3: "gemv_mma", 4: "tc"}
 
 STATUS_NAMES = {0: "OK", 1: "UNSUPPORTED", 2: "BAD_ARGUMENTS", 3: "ALLOC_FAILED", 4: "CUDA_ERROR", 5: "TIMEOUT",
                 6: "NO_DEVICE"}
@@ -62,6 +62,7 @@ EXPORTS = [
     "kudnn_b200_linear_workspace_bytes", "kudnn_b200_shard_range", "kudnn_b200_last_error", "kudnn_b200_version",
     "kudnn_b200_device_count", "kudnn_b200_linear_set_mirrors", "kudnn_b200_peer_buffer_create",
     "kudnn_b200_peer_buffer_open", "kudnn_b200_peer_buffer_close", "kudnn_b200_peer_buffer_destroy",
+    "kudnn_b200_linear_unpack", "kudnn_b200_debug_set_wait", "kudnn_b200_debug_fail_allocation",
 ]
 
 _lib = None
@@ -97,6 +98,9 @@ def library():
     lib.kudnn_b200_peer_buffer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
     lib.kudnn_b200_peer_buffer_close.argtypes = [vp]
     lib.kudnn_b200_peer_buffer_destroy.argtypes = [vp]
+    lib.kudnn_b200_linear_unpack.argtypes = [vp]
+    lib.kudnn_b200_debug_set_wait.argtypes = [vp, ctypes.c_longlong, i32]
+    lib.kudnn_b200_debug_fail_allocation.argtypes = [i32]
     lib.kudnn_b200_linear_force_kernel.argtypes = [vp, i32]
     lib.kudnn_b200_linear_last_kernel.argtypes = [vp]
     lib.kudnn_b200_linear_last_launches.argtypes = [vp]
@@ -198,6 +202,11 @@ def peer_buffer_destroy(ptr):
     _check(library().kudnn_b200_peer_buffer_destroy(ptr))
 
 
+def debug_fail_allocation(nth):
+    """Test hook: the nth (0 = next) device allocation of the library fails; negative switches it off."""
+    _check(library().kudnn_b200_debug_fail_allocation(nth))
+
+
 def run_static_scratch(desc, a, b, c=None, bias=None, res=None, out=None, alpha=1.0, beta=0.0, gamma=1.0, stream=None):
     """Decode-shaped Linear (m <= 16) through the entry point that allocates no device memory.
 
@@ -242,6 +251,14 @@ class Linear:
 
     def prepack(self, b, stream=None):
         _check(self._lib.kudnn_b200_linear_prepack(self._h, _ptr(b), stream))
+
+    def unpack(self):
+        """Forgets the packed weights: later runs read the weight pointer they are given."""
+        _check(self._lib.kudnn_b200_linear_unpack(self._h))
+
+    def debug_set_wait(self, wait_limit_cycles, skip_kblock=-1):
+        """Test hook: limit of the device-side waits in SM cycles, and the k-block whose loads CTA 0 leaves out."""
+        _check(self._lib.kudnn_b200_debug_set_wait(self._h, wait_limit_cycles, skip_kblock))
 
     def run(self, a, b, c=None, bias=None, res=None, out=None, alpha=1.0, beta=0.0, gamma=1.0, stream=None):
         """Device pointers; asynchronous on `stream` (a cudaStream_t value, None = default stream)."""

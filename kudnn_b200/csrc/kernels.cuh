@@ -47,18 +47,6 @@ cudaError_t launch_simt(const LinearProblem &pr, cudaStream_t stream);
 bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPlan *plan);
 cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const GemvWorkspace &ws, cudaStream_t stream);
 
-// Streaming kernel fed through a shared-memory ring (gemv_ring.cu): m <= 16, 16-bit types, k a multiple of 2048.
-struct RingPlan {
-    bool rows16;
-    int grid, ksplit, spg, kc, ctas_per_chunk;
-    long long range, total;
-    size_t smem_bytes;
-    long long partial_floats, counter_count;
-};
-bool gemv_ring_plan(const LinearProblem &pr, int sm_count, RingPlan *plan);
-cudaError_t launch_gemv_ring(const LinearProblem &pr, const RingPlan &plan, const GemvWorkspace &ws, DeviceStatus *status,
-                             cudaStream_t stream);
-
 // Tensor-core kernel.  Operands must be K-major with 16-byte aligned rows; see tc_eligible().
 struct TcOperands {
     const void *a;  // [m, k_total] K-major
@@ -84,8 +72,10 @@ bool tc_available();
 const char *tc_unavailable_reason();
 // with_staging: the launch writes output mirrors and needs the epilogue's row staging in shared memory
 cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm_count, bool with_staging, TcPlan *plan);
+// wait_limit_cycles: SM cycles after which a device-side wait gives up (0 = the default of about two seconds);
+// skip_kblock: test hook for the timeout path, -1 = off (see TcParams::skip_kb).
 cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams &epi, long long m, long long n,
-                      DeviceStatus *status, cudaStream_t stream);
+                      DeviceStatus *status, cudaStream_t stream, long long wait_limit_cycles = 0, int skip_kblock = -1);
 
 // Packing / conversion kernels.
 // dst[r, kk] (row pitch ldd, K-major) = src[r*s_row + kk*s_k] converted to dst_dtype; columns [k, k_pad) are zeroed.

@@ -3,6 +3,7 @@
 #include "kernels.cuh"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -53,6 +54,25 @@ long long span_elems(long long e0, long long s0, long long e1, long long s1, con
     return last + 1;
 }
 
+// Test hook (kudnn_b200_debug_fail_allocation): the n-th device allocation the library attempts from now on fails
+// with cudaErrorMemoryAllocation instead of reaching cudaMalloc; negative = off.
+std::atomic<int> g_alloc_fail_countdown{-1};
+
+cudaError_t device_malloc(void **ptr, size_t bytes)
+{
+    int left = g_alloc_fail_countdown.load();
+    while (left >= 0) {
+        if (g_alloc_fail_countdown.compare_exchange_weak(left, left - 1)) {
+            if (left == 0) {
+                *ptr = nullptr;
+                return cudaErrorMemoryAllocation;
+            }
+            break;
+        }
+    }
+    return cudaMalloc(ptr, bytes);
+}
+
 struct DeviceBuffer {
     void *ptr = nullptr;
     size_t bytes = 0;
@@ -66,7 +86,7 @@ struct DeviceBuffer {
             ptr = nullptr;
             bytes = 0;
         }
-        cudaError_t e = cudaMalloc(&ptr, need);
+        cudaError_t e = device_malloc(&ptr, need);
         if (e == cudaSuccess) {
             bytes = need;
         }
@@ -107,6 +127,12 @@ struct kudnn_b200_linear_s {
     int n_mirrors = 0;
     void *c_mirror[kb::kMaxMirrors] = {};
     void *out_mirror[kb::kMaxMirrors] = {};
+
+    // device-side waits: limit in SM cycles (0 = default) and the timeout test hook (kudnn_b200_debug_set_wait)
+    long long wait_limit = 0;
+    int skip_kblock = -1;
+    cudaStream_t counters_stream = nullptr;  // stream the arrival counters were last zeroed or used on
+    bool counters_dirty = false;             // a kernel that gave up may have left arrival counters set
 
     DeviceBuffer status;        // kb::DeviceStatus
     DeviceBuffer gemv_partials, gemv_counters;
@@ -403,15 +429,22 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
         if (e != cudaSuccess) {
             return fail_cuda(e, "streaming-kernel scratch");
         }
-        if (h->gemv_counters.bytes < static_cast<size_t>(counter_count) * sizeof(unsigned)) {
+        const bool grow = h->gemv_counters.bytes < static_cast<size_t>(counter_count) * sizeof(unsigned);
+        if (grow) {
             e = h->gemv_counters.reserve(static_cast<size_t>(counter_count) * sizeof(unsigned));
             if (e != cudaSuccess) {
                 return fail_cuda(e, "streaming-kernel counters");
             }
+        }
+        // The kernels leave the counters at zero, so they are cleared only when they are new, after a run that gave
+        // up, or when the caller moved to another stream (the clear is then ordered in front of this launch).
+        if (grow || h->counters_dirty || h->counters_stream != stream) {
             e = cudaMemsetAsync(h->gemv_counters.ptr, 0, h->gemv_counters.bytes, stream);
             if (e != cudaSuccess) {
                 return fail_cuda(e, "streaming-kernel counters");
             }
+            h->counters_dirty = false;
+            h->counters_stream = stream;
         }
         ws->partials = static_cast<float *>(h->gemv_partials.ptr);
         ws->counters = static_cast<unsigned *>(h->gemv_counters.ptr);
@@ -419,26 +452,6 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
         ws->counter_count = static_cast<long long>(h->gemv_counters.bytes / sizeof(unsigned));
         return KUDNN_B200_OK;
     };
-    if (forced == KUDNN_B200_KERNEL_GEMV_RING) {
-        // Only on request: bulk copies into a shared-memory ring read HBM slower than plain 16-byte loads on this
-        // GPU (measured without any arithmetic), so the automatic choice never takes this kernel.
-        kb::RingPlan rplan;
-        if (two_d && d.m <= 16 && kb::gemv_ring_plan(pr, h->sm_count, &rplan)) {
-            kb::GemvWorkspace ws;
-            rc = reserve_gemv_scratch(rplan.partial_floats, rplan.counter_count, &ws);
-            if (rc != KUDNN_B200_OK) {
-                return rc;
-            }
-            cudaError_t e = kb::launch_gemv_ring(pr, rplan, ws, static_cast<kb::DeviceStatus *>(h->status.ptr), stream);
-            if (e != cudaSuccess) {
-                return fail_cuda(e, "ring streaming kernel launch");
-            }
-            h->last_kernel = KUDNN_B200_KERNEL_GEMV_RING;
-            h->last_launches = 1;
-            return KUDNN_B200_OK;
-        }
-        return fail(KUDNN_B200_UNSUPPORTED, "the ring streaming kernel needs m <= 16, 16-bit K-contiguous operands and k % 2048 == 0");
-    }
     if (two_d && d.m <= 16 &&
         (forced == KUDNN_B200_KERNEL_AUTO || forced == KUDNN_B200_KERNEL_GEMV_FMA || forced == KUDNN_B200_KERNEL_GEMV_MMA)) {
         kb::GemvPlan plan;
@@ -550,7 +563,8 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
                 }
             }
             cudaError_t e = kb::launch_tc(ops, h->tc_plan, pr.epi, d.m, d.n,
-                                          static_cast<kb::DeviceStatus *>(h->status.ptr), stream);
+                                          static_cast<kb::DeviceStatus *>(h->status.ptr), stream, h->wait_limit,
+                                          h->skip_kblock);
             if (e != cudaSuccess) {
                 return fail_cuda(e, "tensor-core kernel launch");
             }
@@ -592,6 +606,20 @@ bool pipeline_applies(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_a
     if (d.has_bias && d.bias_sm != 0 && (d.bias_sn != 1 || d.bias_sm < d.n)) {
         return false;
     }
+    // Only page-locked buffers overlap: with pageable memory the copy back of block i holds the host until it is
+    // done, so block i+1 would be copied in only afterwards and the blocks would run strictly one after another,
+    // each paying its own launch set-up.  Such callers get the single-shot path.
+    auto pinned = [](const void *p) {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        return attr.type == cudaMemoryTypeHost;
+    };
+    if (!pinned(args.a) || !pinned(d.res_op != KUDNN_B200_RES_NONE ? args.out : args.c)) {
+        return false;
+    }
     const char *off = std::getenv("KUDNN_B200_HOST_PIPELINE");
     return !(off != nullptr && std::strcmp(off, "0") == 0);
 }
@@ -629,6 +657,7 @@ int read_status(Handle *h)
     }
     if (st.code != kb::kErrNone) {
         cudaMemset(h->status.ptr, 0, sizeof(st));
+        h->counters_dirty = true;
         return fail(KUDNN_B200_TIMEOUT, "device-side wait gave up (site %d, block %d)", st.where, st.block);
     }
     return KUDNN_B200_OK;
@@ -820,8 +849,6 @@ int kudnn_b200_linear_create(const kudnn_b200_linear_desc *desc, kudnn_b200_line
             h->forced_kernel = KUDNN_B200_KERNEL_GEMV_FMA;
         } else if (std::strcmp(force, "gemv_mma") == 0) {
             h->forced_kernel = KUDNN_B200_KERNEL_GEMV_MMA;
-        } else if (std::strcmp(force, "gemv_ring") == 0) {
-            h->forced_kernel = KUDNN_B200_KERNEL_GEMV_RING;
         }
     }
     *handle = h;
@@ -1042,16 +1069,7 @@ int kudnn_b200_linear_run_host(kudnn_b200_linear_t h, const kudnn_b200_linear_ar
     if (e != cudaSuccess) {
         return fail_cuda(e, "run_host");
     }
-    kb::DeviceStatus st;
-    e = cudaMemcpy(&st, h->status.ptr, sizeof(st), cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) {
-        return fail_cuda(e, "status read");
-    }
-    if (st.code != kb::kErrNone) {
-        cudaMemset(h->status.ptr, 0, sizeof(st));
-        return fail(KUDNN_B200_TIMEOUT, "device-side wait gave up (site %d, block %d)", st.where, st.block);
-    }
-    return KUDNN_B200_OK;
+    return read_status(h);
 }
 
 int kudnn_b200_linear_run_any(kudnn_b200_linear_t h, const kudnn_b200_linear_args *args, void *cuda_stream)
@@ -1083,21 +1101,12 @@ int kudnn_b200_linear_check(kudnn_b200_linear_t h, void *cuda_stream)
     if (e != cudaSuccess) {
         return fail_cuda(e, "check");
     }
-    kb::DeviceStatus st;
-    e = cudaMemcpy(&st, h->status.ptr, sizeof(st), cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) {
-        return fail_cuda(e, "status read");
-    }
-    if (st.code != kb::kErrNone) {
-        cudaMemset(h->status.ptr, 0, sizeof(st));
-        return fail(KUDNN_B200_TIMEOUT, "device-side wait gave up (site %d, block %d)", st.where, st.block);
-    }
-    return KUDNN_B200_OK;
+    return read_status(h);
 }
 
 int kudnn_b200_linear_force_kernel(kudnn_b200_linear_t h, int kernel)
 {
-    if (h == nullptr || kernel < KUDNN_B200_KERNEL_AUTO || kernel > KUDNN_B200_KERNEL_GEMV_RING) {
+    if (h == nullptr || kernel < KUDNN_B200_KERNEL_AUTO || kernel > KUDNN_B200_KERNEL_TC) {
         return fail(KUDNN_B200_BAD_ARGUMENTS, "force_kernel: bad argument");
     }
     h->forced_kernel = kernel;
@@ -1115,6 +1124,40 @@ int kudnn_b200_linear_set_mirrors(kudnn_b200_linear_t h, int count, void *const 
         h->c_mirror[i] = c_mirrors != nullptr ? c_mirrors[i] : nullptr;
         h->out_mirror[i] = out_mirrors != nullptr ? out_mirrors[i] : nullptr;
     }
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_unpack(kudnn_b200_linear_t h)
+{
+    if (h == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "unpack: null handle");
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    h->packed_key = nullptr;
+    h->packed_ptr = nullptr;
+    h->packed_raw = nullptr;
+    h->packed_ld = h->packed_ktotal = 0;
+    h->plan_valid = false;
+    if (h->device >= 0) {
+        h->b_packed.release();
+    }
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_debug_set_wait(kudnn_b200_linear_t h, long long wait_limit_cycles, int skip_kblock)
+{
+    if (h == nullptr || wait_limit_cycles < 0) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "debug_set_wait: bad argument");
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    h->wait_limit = wait_limit_cycles;
+    h->skip_kblock = skip_kblock;
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_debug_fail_allocation(int nth)
+{
+    g_alloc_fail_countdown.store(nth);
     return KUDNN_B200_OK;
 }
 

@@ -8,8 +8,11 @@
 // kernels' split-K reduction) lives in a fixed array inside this library's device image.
 //
 // Consequences a user has to know:
-//   * the array is part of the module: every GPU that loads the library holds it (about 8 MiB) until the process
-//     exits, whether or not this entry point is ever called;
+//   * the array is part of the library's device code: every GPU on which that code has been loaded holds it (about
+//     8 MiB) until the process exits.  The CUDA runtime loads device code lazily by default, so the array appears
+//     with the first call on a device, and each kernel variant (element type x row-count class) is loaded by the
+//     first call that launches it; both take device memory from the driver, once.  Warm up one call per device and
+//     variant before giving the rest of HBM away (or set CUDA_MODULE_LOADING=EAGER); later calls take none;
 //   * problems whose scratch would not fit are refused with KUDNN_B200_UNSUPPORTED, nothing is launched;
 //   * all calls on one device share the array.  Two calls that overlap on the GPU (different streams, or different
 //     host threads on different streams) race on it and both results are undefined; serialise them on one stream;

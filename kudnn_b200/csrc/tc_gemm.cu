@@ -4,16 +4,16 @@
 // (src/dnn/src/matmul_jit/MatrixComputation/kudnn_default_impl_fp16fp16f32f32.cpp:900-983) and the BLAS calls of
 // src/dnn/src/kudnn_gemm.cpp:157-227.
 //
-// Shape of one CTA (320 threads, persistent over output tiles, one CTA per SM):
-//   warp 0      producer: one lane issues the TMA loads of the A tile [128 x 128 B] and the B tile [rows x 128 B]
-//               of every k-block into the ring (3 or 5 stages), 128-byte swizzle, completion on an mbarrier
-//   warp 1      one lane issues tcgen05.mma (K = 32 bytes per instruction, four per k-block) into one of two TMEM
-//               accumulators and commits to the stage's "empty" barrier / the tile's "full" barrier; the warp also
-//               owns TMEM allocation
-//   warps 2..9  epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; two warps share a lane quarter and
-//               split the columns) 8 columns at a time, applies the post-GEMM chain, collects 128 bytes per row in
-//               shared memory of its own and stores them so that an instruction covers 4 rows x 128 bytes; the
-//               second accumulator lets this overlap the next tile's main loop
+// Shape of one CTA (448 threads, persistent over output tiles, one CTA per SM):
+//   warp 0       producer: one lane issues the TMA loads of the A tile [128 x 128 B] and the B tile [rows x 128 B]
+//                of every k-block into the ring (4 to 6 stages), 128-byte swizzle, completion on an mbarrier
+//   warp 1       one lane issues tcgen05.mma (K = 32 bytes per instruction, four per k-block) into one of two TMEM
+//                accumulators and commits to the stage's "empty" barrier / the tile's "full" barrier; the warp also
+//                owns TMEM allocation
+//   warps 2..13  epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; three warps share a lane quarter and
+//                split the columns) 8 columns at a time, applies the post-GEMM chain and stores 16 bytes per tensor
+//                straight from registers (with output mirrors: 128-byte row pieces collected in shared memory); the
+//                second accumulator lets this overlap the next tile's main loop
 // Three launch shapes (tc_make_plan): clusters of two CTAs on 256 x 256 tiles with cta_group::2 MMAs (large
 // problems), single CTAs on 128 x 256 / 128 x 128 tiles, and clusters of 2-8 CTAs that cut K of one 128 x 128 tile
 // and add their partial tiles through distributed shared memory (few tiles, long K).
@@ -34,24 +34,6 @@
 #include <cstring>
 #include <mutex>
 
-// Optional phase timestamps for tuning (build with -DKUDNN_B200_TC_TRACE): a few threads per CTA write %globaltimer
-// at role boundaries into a device array that kudnn_b200_debug_tc_trace copies out.  Not part of the product build.
-#ifdef KUDNN_B200_TC_TRACE
-__device__ long long g_tc_trace[160 * 16];
-#define TC_TRACE(slot)                                                                             \
-    do {                                                                                           \
-        long long t_;                                                                              \
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                     \
-        g_tc_trace[blockIdx.x * 16 + (slot)] = t_;                                                 \
-    } while (0)
-extern "C" int kudnn_b200_debug_tc_trace(long long *out)
-{
-    return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 160 * 16));
-}
-#else
-#define TC_TRACE(slot) do { } while (0)
-#endif
-
 namespace kb {
 
 namespace {
@@ -62,7 +44,7 @@ constexpr int kTcThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA, th
 constexpr int kStageRowBytes = 128;  // one swizzle row: 64 16-bit or 32 32-bit elements
 constexpr int kABytes = kBM * kStageRowBytes;
 constexpr int kMaxGroupM = 16;  // most tile rows per raster group
-constexpr long long kWaitLimitCycles = 4000000000ll;  // about two seconds at 2 GHz
+constexpr long long kDefaultWaitLimitCycles = 4000000000ll;  // about two seconds at 2 GHz
 constexpr int kWarpBiasFloats = 128;  // per epilogue warp: the bias values of its columns of the current tile, as fp32
 constexpr int kWarpStageBytes = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes of output on their way to memory
 // after the stage ring: barriers and flags (256 bytes), the bias slices; then, if present, the output staging
@@ -86,6 +68,10 @@ struct TcParams {
     // so that a last wave that would keep fewer than half the pairs busy is spread over twice as many
     int num_items, narrow_from;
     unsigned idesc_narrow;
+    long long wait_limit;  // SM cycles after which a wait on an mbarrier gives up
+    // Test hook for the timeout path: the producer of CTA 0 leaves out the loads of this k-block of its first work
+    // item (-1 = never), so the MMA thread's wait for that stage runs into wait_limit.  Nothing faults or hangs.
+    int skip_kb;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -124,7 +110,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 // counted on the SM's own cycle counter, which is cheap to read; the wall-clock timer is not (a read costs about a
 // microsecond, which would sit on the critical path of every k-block).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          DeviceStatus *status, int where)
+                                          DeviceStatus *status, int where, long long limit)
 {
 #pragma unroll 1
     for (int i = 0; i < 128; ++i) {
@@ -142,7 +128,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
             if (*abort_flag != 0) {
                 return false;
             }
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 if (atomicCAS(&status->code, kErrNone, kErrTimeout) == kErrNone) {
                     status->where = where;
@@ -385,8 +371,8 @@ __device__ __forceinline__ bool vec_ok(const void *base, int dtype, long long id
 // Post-GEMM chain and stores for 8 consecutive columns of one output row, starting at column ni.  Same arithmetic
 // as finish_element(), but organised as passes over the 8 values: every run-time switch (element type, bias,
 // second output) is tested once per pass instead of once per element, which leaves straight-line code with eight
-// independent dependency chains.  Only four warps run the epilogue, one per scheduler, so that instruction-level
-// parallelism is what hides the arithmetic latency.
+// independent dependency chains: with three epilogue warps per scheduler, instruction-level parallelism is what
+// hides the arithmetic latency.
 template <int kAct, int kPrecise>
 __device__ __forceinline__ void epilogue_group8(const EpiParams &e, const uint32_t (&raw)[8], long long mi, long long ni)
 {
@@ -1103,9 +1089,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         }
     }
-    if (threadIdx.x == 0) {
-        TC_TRACE(0);
-    }
     tc_fence_before();
     __syncthreads();
     if (kPair) {
@@ -1113,9 +1096,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     }
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) {
-        TC_TRACE(1);
-    }
     // work items: tiles (x splits) over CTAs, or pair tiles over clusters of two
     const uint32_t pair_rank = kPair ? cluster_rank() : 0u;
     const int first_item = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
@@ -1145,13 +1125,15 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 const int tm = kPair ? 2 * (first_m + in_group % gsize) + static_cast<int>(pair_rank)
                                      : first_m + in_group % gsize;
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
-                    if (!mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag, p.status, 1)) {
+                    if (!mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag, p.status, 1, p.wait_limit)) {
                         alive = false;
                         break;
                     }
                     unsigned char *sa = smem + stage * kStageBytes;
                     unsigned char *sb = sa + kABytes;
-                    if (kPair) {
+                    if (kb == p.skip_kb && blockIdx.x == 0 && item == first_item) {
+                        // test hook: this stage is never filled
+                    } else if (kPair) {
                         // both CTAs' bytes are counted on the leader's barrier; only the leader announces them
                         if (pair_rank == 0) {
                             mbar_expect_tx(full_bar + stage, 2 * kStageBytes);
@@ -1172,7 +1154,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                     }
                 }
             }
-            TC_TRACE(2);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -1189,13 +1170,13 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 const uint32_t idesc = (width == kBN) ? p.idesc : p.idesc_narrow;
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
-                if (!mbar_wait(tmem_empty + acc, acc_phase ^ 1u, abort_flag, p.status, 2)) {
+                if (!mbar_wait(tmem_empty + acc, acc_phase ^ 1u, abort_flag, p.status, 2, p.wait_limit)) {
                     break;
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBN);
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
-                    if (!mbar_wait(full_bar + stage, phase, abort_flag, p.status, 3)) {
+                    if (!mbar_wait(full_bar + stage, phase, abort_flag, p.status, 3, p.wait_limit)) {
                         alive = false;
                         break;
                     }
@@ -1233,7 +1214,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 } else {
                     umma_commit(tmem_full + acc);
                 }
-                TC_TRACE(3);
                 acc ^= 1;
                 if (acc == 0) {
                     acc_phase ^= 1u;
@@ -1287,10 +1267,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 __syncwarp();
                 staged_bias = warp_bias;
             }
-            const bool arrived = mbar_wait(tmem_full + acc, acc_phase, abort_flag, p.status, 4);
-            if (threadIdx.x == 64) {
-                TC_TRACE(4);
-            }
+            // every lane waits on its own and may see the abort flag at a different poll: agree on one answer before
+            // the warp-wide tensor-memory instructions below
+            const bool arrived =
+                __all_sync(0xffffffffu, mbar_wait(tmem_full + acc, acc_phase, abort_flag, p.status, 4, p.wait_limit));
             if (!arrived && p.splits == 1) {
                 break;
             }
@@ -1312,9 +1292,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                     if (lane == 0) {
                         mbar_arrive(tmem_empty + acc);
                     }
-                }
-                if (threadIdx.x == 64) {
-                    TC_TRACE(5);
                 }
                 break;  // one work item per CTA in this mode
             }
@@ -1350,26 +1327,17 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                     mbar_arrive(tmem_empty + acc);
                 }
             }
-            if (threadIdx.x == 64) {
-                TC_TRACE(10);
-            }
             acc ^= 1;
             if (acc == 0) {
                 acc_phase ^= 1u;
             }
         }
     }
-    if (threadIdx.x == 0) {
-        TC_TRACE(11);
-    }
 
     if (p.splits > 1) {
         // ------------------------------------------------------------------ split-K: add the cluster's partial tiles
         __syncwarp();
         cluster_sync_all();  // all partial tiles are in place (a hardware barrier over every thread of the cluster)
-        if (threadIdx.x == 64) {
-            TC_TRACE(6);
-        }
         if (warp >= 2 && *abort_flag == 0) {
             const int tile = static_cast<int>(blockIdx.x) / p.splits;
             const int per_group = p.group_m * p.tiles_n;
@@ -1403,9 +1371,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                     break;
             }
         }
-        if (threadIdx.x == 64) {
-            TC_TRACE(7);
-        }
         __syncwarp();
         cluster_sync_all();  // no CTA leaves while another still reads its shared memory
     }
@@ -1434,9 +1399,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         } else {
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
         }
-    }
-    if (threadIdx.x == 0) {
-        TC_TRACE(12);
     }
 }
 
@@ -1655,10 +1617,13 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
 }
 
 cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams &epi, long long m, long long n,
-                      DeviceStatus *status, cudaStream_t stream)
+                      DeviceStatus *status, cudaStream_t stream, long long wait_limit_cycles, int skip_kblock)
 {
     TcParams p;
     p.epi = epi;
+    p.wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : kDefaultWaitLimitCycles;
+    // the test hook is honoured by the plain single-CTA shape only (no cluster partner is left half-signalled)
+    p.skip_kb = (plan.pair == 0 && plan.splits == 1) ? skip_kblock : -1;
     p.m = static_cast<int>(m);
     p.n = static_cast<int>(n);
     const int elems_per_row = kStageRowBytes / dtype_size(ops.kind);

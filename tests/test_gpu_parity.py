@@ -67,7 +67,7 @@ def test_batched_shared_weights_run_as_rows(cuda_device, dtype, batch, m, expect
                 b_bcast=True, x_dist="normal", w_std=0.03, seed=25)
     info = helpers.parity(case, cuda_device, acc=ko.ACC_F64, expect_kernel=None if expect == "streaming" else expect)
     if expect == "streaming":  # four rows: one of the streaming kernels, whichever the dispatcher prefers
-        assert info["kernel"] in [kb.KERNEL_NAMES[i] for i in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA, kb.KERNEL_GEMV_RING)]
+        assert info["kernel"] in [kb.KERNEL_NAMES[i] for i in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA)]
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
@@ -114,15 +114,6 @@ def test_gemv_mma_sixteen_rows_shapes(cuda_device, monkeypatch, wide, n, k):
     helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_MMA, expect_kernel=kb.KERNEL_GEMV_MMA)
 
 
-@pytest.mark.parametrize("dtype", ["f16", "bf16"])
-@pytest.mark.parametrize("m", [1, 4, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(1003, 2048), (520, 4096), (300, 8192), (8, 2048), (2600, 16384)])
-def test_gemv_ring(cuda_device, dtype, m, n, k):
-    case = dict(m=m, n=n, k=k, dtype=dtype, bias="row", act=kb.ACT_SWISH, res_op=kb.RES_ELTWISE_MUL, x_dist="normal",
-                w_std=0.02, seed=35)
-    helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_RING, expect_kernel=kb.KERNEL_GEMV_RING)
-
-
 @pytest.mark.parametrize("m", [4, 16])
 def test_decode_default_is_deterministic(cuda_device, m):
     case = dict(m=m, n=4096, k=4096, dtype="bf16", res_op=kb.RES_ELTWISE_MUL, x_dist="normal", w_std=0.02, seed=36)
@@ -155,7 +146,7 @@ def test_gemv_repeated_calls_leave_counters_clean(cuda_device):
         lin.run(d["a"], d["b"], t_c, None, d["res"], t_o, stream=torch.cuda.current_stream().cuda_stream)
         lin.check(stream=torch.cuda.current_stream().cuda_stream)
         outs.append(helpers._from_torch(t_o))
-    assert lin.last_kernel in (kb.KERNEL_GEMV_MMA, kb.KERNEL_GEMV_RING)
+    assert lin.last_kernel in (kb.KERNEL_GEMV_MMA,)
     helpers.compare(outs[0], ref_o, desc.out_dtype)
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])  # slot-ordered sums: deterministic
 
@@ -208,8 +199,9 @@ def test_tc_alpha_beta(cuda_device):
 @pytest.mark.parametrize("splits", [None, "1", "3", "64"])
 @pytest.mark.parametrize("m,n,k", [(128, 1024, 1024), (100, 200, 2056), (300, 130, 1000)])
 def test_tc_split_k(cuda_device, monkeypatch, dtype, splits, m, n, k):
-    """Few tiles and a long K: K is cut over several CTAs, partial tiles meet in scratch, the last arriver finishes.
-    The result must not depend on the cut beyond fp32 summation order, and repeated calls must agree bit for bit."""
+    """Few tiles and a long K: the CTAs of a cluster cut K between them, keep their partial tiles in shared memory and
+    add them in rank order through distributed shared memory.  The result must not depend on the cut beyond fp32
+    summation order, and repeated calls must agree bit for bit."""
     if splits is not None:
         monkeypatch.setenv("KUDNN_B200_TC_SPLITS", splits)
     case = dict(m=m, n=n, k=k, dtype=dtype, bias="row", act=kb.ACT_SWISH, res_op=kb.RES_EXT, gamma=0.5, x_dist="normal",
@@ -375,7 +367,7 @@ def test_config4_decode_gate_full(cuda_device, m):
     lin = kb.Linear(desc)
     lin.run(x, w, None, None, gate, out, stream=torch.cuda.current_stream().cuda_stream)
     lin.check(stream=torch.cuda.current_stream().cuda_stream)
-    assert lin.last_kernel in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA, kb.KERNEL_GEMV_RING)
+    assert lin.last_kernel in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA)
     info = _check_rows(desc, x, w, None, gate, None, out, list(range(m)))
     assert info["out"]["bit_exact_fraction"] > 0.98
 

@@ -1,18 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the Linear(+post-op) hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5m] [--impl ours|reference]
 
-A step is one Linear+post-op call over one batch of synthetic input.  The default workload is the bf16 prefill
-FFN up-projection (x[4096,4096] . W[11008,4096]^T + b, SiLU).  With N > 1 (launched by torch.distributed.run, one
-process per GPU) every rank runs the same per-GPU batch against replicated weights: the m-sharded layout, no
-collective on the data path, weak scaling.  `--workload c5m` is the strong-scaling form (32768 rows split over
-the ranks), `--workload c5n` the column-sharded form with an NCCL all-gather of the output.
+A step is one Linear+post-op call over one batch of synthetic input.  The default workload, at every N, is the large
+sharded prefill layer (x[32768,8192] . W[28672,8192]^T + b, SiLU, bf16) with its rows split over the N ranks and the
+weights replicated (`c5m`): no collective on the data path, strong scaling, and at N = 1 the whole layer on one GPU.
+`--workload c5n` is the column-sharded form in which every rank ends with the full output; `c1` .. `c4` are the
+other benchmark configurations (at N > 1 they run as replicas).
 
 Rank 0 prints one JSON line.  `value` is device-timed throughput with inputs resident in HBM; `e2e` is the same
 metric through the host-pointer entry point of the C ABI with the host<->device copies inside the timed region;
-`roofline` relates the kernel to the measured peaks of this GPU pool; `cpu_baseline` is the CPU restatement of the
-reference path timed on this machine's cores.  `--impl reference` times that CPU path alone.
+`roofline` relates the kernel to the measured peaks of this GPU pool; at N = 1 `configs` holds the other four
+configurations (time, rate, fraction of the measured peak, kernel), `cublas_compare` a library GEMM of the same
+shape timed the same way (a comparison leg only), and `cpu_baseline` the CPU restatement of the reference path timed
+on this machine's cores.  `--impl reference` times that CPU path alone.
 """
 import argparse
 import json
@@ -51,6 +53,20 @@ NCU_TRAFFIC_BYTES = {
     # sums); scaled to n = 28672 by the rows
     "c4": 471.9e6 + 11.5e6,
 }
+
+
+def c5m_traffic_bytes(rows):
+    """DRAM bytes per launch of the tensor-core kernel on `rows` rows of the large prefill layer, from an ncu capture
+    of the 4096-row case (see NCU_C5M below): x and y move once, W is streamed once per raster group of tile rows."""
+    if NCU_C5M is None:
+        return None
+    per_group_rows, w_bytes_per_group, xy_bytes_per_row = NCU_C5M
+    groups = -(-rows // per_group_rows)
+    return groups * w_bytes_per_group + rows * xy_bytes_per_row
+
+
+# (rows per raster group, DRAM bytes of W per group, DRAM bytes of x and y per row); None until captured
+NCU_C5M = None
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -254,6 +270,18 @@ class CpuArm:
         return 2.0 * rows * self.w["n"] * self.w["k"] / t / 1e12, rows, t
 
 
+def config_block(w, wname, world):
+    """What the run is about; identical in both arms.  How each arm ran it is in the line's `details`."""
+    if wname == "c5m":
+        par = "rows of x split over %d rank(s), weights replicated, no collective" % world
+    elif wname == "c5n":
+        par = "columns of W split over %d rank(s), every rank ends with the full y" % world
+    else:
+        par = "single GPU" if world == 1 else "%d replicas of the full batch" % world
+    return {"workload": wname + ": " + w["label"], "m": w["m"], "n": w["n"], "k": w["k"], "dtype": w["dtype"],
+            "parallelism": par}
+
+
 def run_reference_arm(args, w, wname, rank):
     """--impl reference: the CPU path alone, all host threads, bounded sample per step."""
     if rank != 0:
@@ -273,10 +301,12 @@ def run_reference_arm(args, w, wname, rank):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(x[2] for x in times) / len(times),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": wname + ": " + w["label"],
-                   "note": "KuDNN itself needs aarch64 SVE/SME and the closed KML BLAS; this arm times the scalar-"
-                           "semantics C restatement of its Linear path (oracle/kudnn_linear_oracle.c)"},
+        "higher_is_better": True, "scaling": "strong" if wname.startswith("c5") else "weak", "vs_baseline": None,
+        "dtype": w["dtype"], "data": "synthetic",
+        "config": config_block(w, wname, args.gpus),
+        "details": {"note": "KuDNN itself needs aarch64 SVE/SME and the closed KML BLAS; this arm times the scalar-"
+                            "semantics C restatement of its Linear path (oracle/kudnn_linear_oracle.c) on rank 0's "
+                            "host cores"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": best[3], "kind": "port",
                          "sample": "%d of %d rows of x per step, full W (weight conversion included), built %s"
                                    % (rows, w["m"], arm.build)},
@@ -314,7 +344,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5m", "c5n"])
+    ap.add_argument("--workload", default="c5m", choices=["c1", "c2", "c3", "c4", "c5m", "c5n"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=0, help="override the row count (c4: 1, 4 or 16)")
     ap.add_argument("--n", type=int, default=0, help="override the column count (smaller cases for profiler captures)")
@@ -472,7 +502,8 @@ def main():
         long_step = my_ms >= 5.0
         tensor_peak = peaks["bf16_tflops_sustained"] if long_step else peaks["bf16_tflops"]
         roofline = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
-                    "frac": achieved / tensor_peak, "traffic": NCU_TRAFFIC_BYTES.get(wname),
+                    "frac": achieved / tensor_peak,
+                    "traffic": c5m_traffic_bytes(m_local) if wname == "c5m" else NCU_TRAFFIC_BYTES.get(wname),
                     "peak_source": peak_kind + (" (cuBLAS bf16 sustained: a %.1f ms step runs under the power cap; burst %.1f)"
                                                 % (my_ms, peaks["bf16_tflops"]) if long_step else
                                                 " (cuBLAS bf16 burst; sustained %.1f)" % peaks["bf16_tflops_sustained"]),
@@ -484,10 +515,13 @@ def main():
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
         "dtype": w["dtype"], "data": "synthetic (seeded; shapes and distributions of the named configuration)",
-        "config": {"workload": wname + ": " + w["label"], "rows_per_gpu": m_local, "cols_per_gpu": n_local,
-                   "parallelism": par, "l2": "256 MiB written, then 256 MiB of another buffer read (L2 left clean), between steps and outside the timed event pairs",
-                   "timing": "CUDA events around every step on the launching stream, summed; max over ranks",
-                   "weights": "pre-packed once at set-up (for K-major 16-bit weights the caller's buffer is used as is)"},
+        "config": config_block(w, wname, world),
+        "details": {"rows_per_gpu": m_local, "cols_per_gpu": n_local, "parallelism": par,
+                    "l2": "256 MiB written, then 256 MiB of another buffer read (L2 left clean), between steps and "
+                          "outside the timed event pairs",
+                    "timing": "CUDA events around every step on the launching stream, summed; max over ranks",
+                    "weights": "pre-packed once at set-up (for K-major 16-bit weights the caller's buffer is used as "
+                               "is)"},
         "roofline": roofline,
         "gpu_launches": launches[0],
         "clocks": sampler.summary(t0, t1),
@@ -496,7 +530,13 @@ def main():
     # ---- extras on a single GPU: e2e through host pointers, decode GEMV, CPU baseline
     if world == 1 and not args.no_extras:
         line["e2e"] = e2e_leg(torch, kb, w, wname, m_local, device, min(args.steps, 10))
-        if wname == "c2":
+        if wname == "c5m":
+            mhz = line["clocks"].get("sm_mhz")
+            line["roofline"]["ms_x_mhz"] = my_ms * mhz if mhz else None
+            line["cublas_compare"] = cublas_leg(torch, x, wt, peaks, flush, local_rank, min(args.steps, 20))
+            x = wt = y = bias = None  # the 2.9 GB of this workload make room for the other configurations
+            torch.cuda.empty_cache()
+            line["configs"] = other_configs_leg(torch, kb, device, peaks, flush)
             line["decode_gemv"] = gemv_leg(torch, kb, device, peaks, flush)
         try:
             arm = CpuArm(w)
@@ -571,6 +611,61 @@ def e2e_leg(torch, kb, w, wname, m, device, steps, sync=None):
                 "d2h_bytes_per_step": d2h, "ms_per_step": dt * 1e3}
     return {"value": flops(w, m) / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "ms_per_step": dt * 1e3, "timing": "host clock around run_host calls, which return after the D2H copy"}
+
+
+def cublas_leg(torch, x, wt, peaks, flush, gpu_index, steps):
+    """Comparison only, never on the product path: torch.matmul (a library GEMM, no bias, no activation) on the same
+    x and W, timed like the product step, with the SM clock sampled meanwhile.  time x clock says whether a gap
+    between the two is cycles or power."""
+    y = torch.empty(x.shape[0], wt.shape[0], device=x.device, dtype=x.dtype)
+    wt_t = wt.t()
+    sampler = ClockSampler(gpu_index)
+    sampler.start()
+    for _ in range(3):
+        flush()
+        torch.matmul(x, wt_t, out=y)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ms = timed_steps(torch, lambda: torch.matmul(x, wt_t, out=y), steps, 0, flush)
+    t1 = time.perf_counter()
+    sampler.stop()
+    clocks = sampler.summary(t0, t1)
+    my_ms = sum(ms) / len(ms)
+    tf = 2.0 * x.shape[0] * wt.shape[0] * x.shape[1] / (my_ms * 1e-3) / 1e12
+    return {"what": "torch.matmul(x, W^T), bf16, no bias or activation (cuBLAS); comparison leg", "ms_per_step": my_ms,
+            "tflops": tf, "frac_of_sustained_peak": tf / peaks["bf16_tflops_sustained"], "sm_mhz": clocks.get("sm_mhz"),
+            "reasons": clocks.get("reasons"),
+            "ms_x_mhz": my_ms * clocks["sm_mhz"] if clocks.get("sm_mhz") else None}
+
+
+def other_configs_leg(torch, kb, device, peaks, flush):
+    """Configurations 1, 2 and 3 on one GPU: time, rate, fraction of the measured burst peak, kernel."""
+    out = {}
+    stream = torch.cuda.current_stream().cuda_stream
+    for name in ("c1", "c2", "c3"):
+        w = dict(WORKLOADS[name])
+        x, wt, bias, res = make_inputs(w, w["m"], device, seed=0)
+        y = torch.empty(w["m"], w["n"], device=device, dtype=x.dtype)
+        lin = kb.Linear(make_desc(kb, w, w["m"]))
+        lin.prepack(wt, stream=stream)
+        if w["res"]:
+            fn = lambda: lin.run(x, wt, None, bias, res, y, stream=stream)
+        else:
+            fn = lambda: lin.run(x, wt, y, bias, stream=stream)
+        ms = timed_steps(torch, fn, 30, 5, flush)
+        lin.check(stream=stream)
+        ms.sort()
+        med = ms[len(ms) // 2]
+        tf = flops(w) / (med * 1e-3) / 1e12
+        out[name] = {"workload": w["label"], "us": med * 1e3, "tflops": tf,
+                     "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+                     "kernel": kb.KERNEL_NAMES.get(lin.last_kernel), "launches_per_call": lin.last_launches,
+                     "algorithmic_flops": flops(w), "algorithmic_bytes": algorithmic_bytes(w)}
+        if name == "c1":
+            out[name]["note"] = "latency-bound: 0.27 GFLOP and 5.2 MB per call"
+        del x, wt, bias, res, y, lin
+        torch.cuda.empty_cache()
+    return out
 
 
 def gemv_leg(torch, kb, device, peaks, flush):

@@ -2,7 +2,8 @@
 // activation, second output) and the parameter blocks every kernel family consumes.
 //
 // The chain follows the order and rounding modes of the reference library:
-//   bias / rounding   src/dnn/src/kudnn_gemm.cpp:157-227 (fp32: add; fp16: round, add in fp16; bf16: add in fp32, RNE)
+//   bias / rounding   src/dnn/src/kudnn_gemm.cpp:157-227 (fp32: add; fp16: round, add in fp16; bf16: add in fp32, RNE;
+//                     fp16 result with a wider bias: add in fp32, one RNE, :348-360 and :679-692)
 //   activation        src/dnn/src/kudnn_linear_activationlayer.cpp:40-56 on the rounded value, fp32 math,
 //                     fp16 result RNE, bf16 result truncated (src/dnn/src/kernels/vml/vml_sve_base.h:111-118)
 //   second output     src/dnn/src/kudnn_linear_res.cpp:57-122 (RNE)
@@ -88,14 +89,26 @@ __device__ __forceinline__ float round_rne(float v, int dtype)
     return __bfloat162float(__float2bfloat16_rn(v));
 }
 
+// The reference's bf16 relu turns a finite result that would round to infinity (magnitude pattern 0x7f7f8000 or
+// above) into infinity before it truncates (src/dnn/src/kernels/vml/vml_sve_base.h:97-109).  Only a negative slope
+// can produce such a value from a bf16 input.
+__device__ __forceinline__ float relu_bf16_overflow(float v)
+{
+    const unsigned u = __float_as_uint(v), mag = u & 0x7fffffffu;
+    return (mag >= 0x7f7f8000u && mag < 0x7f800000u) ? __uint_as_float((u & 0x80000000u) | 0x7f800000u) : v;
+}
+
 // value held after storing an activation result: fp16 RNE, bf16 truncation
-__device__ __forceinline__ float round_act(float v, int dtype)
+__device__ __forceinline__ float round_act(float v, int dtype, int act = KUDNN_B200_ACT_NONE, float act_alpha = 0.0f)
 {
     if (dtype == KUDNN_B200_F32) {
         return v;
     }
     if (dtype == KUDNN_B200_F16) {
         return __half2float(__float2half_rn(v));
+    }
+    if (act == KUDNN_B200_ACT_RELU && act_alpha != 0.0f) {
+        v = relu_bf16_overflow(v);
     }
     return __uint_as_float(__float_as_uint(v) & 0xffff0000u);
 }
@@ -189,12 +202,13 @@ __device__ __forceinline__ EpiResult finish_element(const EpiParams &p, float ac
         t += p.beta * c_old;
     }
     float c1;
-    if (ct == KUDNN_B200_F16) {
+    if (ct == KUDNN_B200_F16 && (!p.has_bias || p.bias_dtype == KUDNN_B200_F16)) {
         c1 = round_rne(t, KUDNN_B200_F16);
         if (p.has_bias) {
             c1 = round_rne(c1 + bias, KUDNN_B200_F16);
         }
     } else {
+        // fp32 and bf16 results, and fp16 results with a wider bias: the bias is added in fp32, one rounding
         if (p.has_bias) {
             t += bias;
         }
@@ -203,7 +217,7 @@ __device__ __forceinline__ EpiResult finish_element(const EpiParams &p, float ac
     float c2 = c1;
     if (kAct < 0) {
         if (p.act != KUDNN_B200_ACT_NONE) {
-            c2 = round_act(activation_any(c1, p.act, p.act_alpha, ct == KUDNN_B200_F32 ? 1 : 0), ct);
+            c2 = round_act(activation_any(c1, p.act, p.act_alpha, ct == KUDNN_B200_F32 ? 1 : 0), ct, p.act, p.act_alpha);
         }
     } else if (kAct != KUDNN_B200_ACT_NONE) {
         float a;
@@ -214,7 +228,7 @@ __device__ __forceinline__ EpiResult finish_element(const EpiParams &p, float ac
         } else {
             a = (ct == KUDNN_B200_F32) ? activation<true>(c1, kAct, p.act_alpha) : activation<false>(c1, kAct, p.act_alpha);
         }
-        c2 = round_act(a, ct);
+        c2 = round_act(a, ct, kAct, p.act_alpha);
     }
     EpiResult r;
     r.c = c2;

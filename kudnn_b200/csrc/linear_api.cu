@@ -218,6 +218,12 @@ void fill_epi(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, 
     e->out_sn = d.out_sn;
     e->alpha = a.alpha;
     e->beta = a.beta;
+    if (d.a_dtype == KUDNN_B200_BF16 && d.b_dtype == KUDNN_B200_BF16 && d.c_dtype == KUDNN_B200_BF16 && d.has_bias == 0) {
+        // the reference's bias-free bf16 product is cblas_bgemm, which takes its scalars as bf16
+        // (src/dnn/src/kudnn_gemm.cpp:222-226)
+        e->alpha = __bfloat162float(__float2bfloat16_rn(a.alpha));
+        e->beta = __bfloat162float(__float2bfloat16_rn(a.beta));
+    }
     e->gamma = a.gamma;
     e->act_alpha = d.act_alpha;
     e->c_dtype = d.c_dtype;

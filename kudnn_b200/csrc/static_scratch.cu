@@ -141,6 +141,11 @@ extern "C" int kudnn_b200_linear_run_static_scratch(const kudnn_b200_linear_desc
     e.out_sn = d.out_sn;
     e.alpha = args->alpha;
     e.beta = args->beta;
+    if (d.a_dtype == KUDNN_B200_BF16 && d.b_dtype == KUDNN_B200_BF16 && d.c_dtype == KUDNN_B200_BF16 && d.has_bias == 0) {
+        // as in the handle-based entry points: the reference's bias-free bf16 product takes bf16 scalars
+        e.alpha = __bfloat162float(__float2bfloat16_rn(args->alpha));
+        e.beta = __bfloat162float(__float2bfloat16_rn(args->beta));
+    }
     e.gamma = args->gamma;
     e.act_alpha = d.act_alpha;
     e.c_dtype = d.c_dtype;

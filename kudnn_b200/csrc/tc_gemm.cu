@@ -400,7 +400,7 @@ __device__ __forceinline__ void epilogue_group8(const EpiParams &e, const uint32
         const long long ib = mi * e.bias_sm + ni * e.bias_sn;
         load8(e.bias, e.bias_dtype, ib, e.bias_sn, full8 && vec_ok(e.bias, e.bias_dtype, ib, e.bias_sn), valid, side);
     }
-    if (ct == KUDNN_B200_F16) {
+    if (ct == KUDNN_B200_F16 && (!e.has_bias || e.bias_dtype == KUDNN_B200_F16)) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             v[j] = __half2float(__float2half_rn(v[j]));
@@ -423,6 +423,11 @@ __device__ __forceinline__ void epilogue_group8(const EpiParams &e, const uint32
             for (int j = 0; j < 8; ++j) {
                 v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
             }
+        } else if (ct == KUDNN_B200_F16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = __half2float(__float2half_rn(v[j]));
+            }
         }
     }
     if (kAct != KUDNN_B200_ACT_NONE) {
@@ -444,6 +449,12 @@ __device__ __forceinline__ void epilogue_group8(const EpiParams &e, const uint32
                 v[j] = __half2float(__float2half_rn(v[j]));
             }
         } else if (ct == KUDNN_B200_BF16) {
+            if ((kAct < 0 ? e.act : kAct) == KUDNN_B200_ACT_RELU && e.act_alpha != 0.0f) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = relu_bf16_overflow(v[j]);
+                }
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 v[j] = __uint_as_float(__float_as_uint(v[j]) & 0xffff0000u);
@@ -607,7 +618,7 @@ __device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32
             side[j] = rp.bias_scalar;
         }
     }
-    if (ct == KUDNN_B200_F16) {
+    if (ct == KUDNN_B200_F16 && (kDt > 0 || rp.bias_mode == 0 || e.bias_dtype == KUDNN_B200_F16)) {
         round_rne8<KUDNN_B200_F16>(v);
         if (rp.bias_mode != 0) {
 #pragma unroll
@@ -625,6 +636,8 @@ __device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32
         }
         if (ct == KUDNN_B200_BF16) {
             round_rne8<KUDNN_B200_BF16>(v);
+        } else if (ct == KUDNN_B200_F16) {
+            round_rne8<KUDNN_B200_F16>(v);
         }
     }
     if (kAct != KUDNN_B200_ACT_NONE) {
@@ -643,6 +656,12 @@ __device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32
         if (ct == KUDNN_B200_F16) {
             round_rne8<KUDNN_B200_F16>(v);
         } else if (ct == KUDNN_B200_BF16) {
+            if ((kAct < 0 ? e.act : kAct) == KUDNN_B200_ACT_RELU && e.act_alpha != 0.0f) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = relu_bf16_overflow(v[j]);
+                }
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 v[j] = __uint_as_float(__float_as_uint(v[j]) & 0xffff0000u);

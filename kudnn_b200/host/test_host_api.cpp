@@ -653,6 +653,35 @@ void ExtensionCases()
     }
 }
 
+// Error convention on the device side (the reference's is src/dnn/src/service.cpp:32-46, 418-431): an allocation
+// that fails inside Run surfaces as Service::BadAlloc, and the object stays usable afterwards.
+void FailurePathCases()
+{
+    const Element::TypeT type = Element::TypeT::F32;
+    const size_t m = 64, k = 48, n = 80;
+    TensorInfo src({m, k}, type, Layout::AB), wei({k, n}, type, Layout::AB), dst({m, n}, type, Layout::AB);
+    std::mt19937 rng(91);
+    HostTensor a = MakeTensor(m * k, type, &rng), w = MakeTensor(k * n, type, &rng), c = MakeTensor(m * n, type, nullptr);
+    Gemm op(src, wei, dst);
+    kudnn_b200_debug_fail_allocation(0);
+    ExpectThrow<Service::BadAlloc>("Gemm.Run_device_allocation_failure_is_BadAlloc",
+                                   [&]() { op.Run(a.data(), w.data(), c.data(), 1.0f, 0.0f, 0); });
+    kudnn_b200_debug_fail_allocation(-1);
+    ExpectNoThrow("Gemm.Run_after_allocation_failure", [&]() { op.Run(a.data(), w.data(), c.data(), 1.0f, 0.0f, 0); });
+    ReadBack(&c);
+    double worst = 0.0;
+    for (size_t i = 0; i < m; ++i) {
+        for (size_t j = 0; j < n; ++j) {
+            double acc = 0.0;
+            for (size_t kk = 0; kk < k; ++kk) {
+                acc += static_cast<double>(a.values[i * k + kk]) * w.values[kk * n + j];
+            }
+            worst = std::max(worst, std::fabs(c.values[i * n + j] - acc));
+        }
+    }
+    Report("Gemm.Run_after_allocation_failure_values", worst <= 1e-4, "worst " + std::to_string(worst));
+}
+
 void NumericTests()
 {
     const Element::TypeT types[3] = {Element::TypeT::F32, Element::TypeT::F16, Element::TypeT::BF16};
@@ -686,6 +715,7 @@ void NumericTests()
         }
     }
     ExtensionCases();
+    FailurePathCases();
 }
 
 }  // namespace

@@ -271,16 +271,23 @@ float ko_activation(float x, int act, float alpha)
     }
 }
 
-/* rounding of an activation result into the storage type: f16 RNE, bf16 truncation */
-static inline float ko_round_act(float v, int dtype)
+/* rounding of an activation result into the storage type: f16 RNE, bf16 truncation.  The bf16 relu kernel first
+ * turns a finite result whose magnitude pattern is 0x7f7f8000 or above (it would round to infinity) into infinity
+ * (vml_sve_base.h:97-109, relu/relu.c:229-232). */
+static inline float ko_round_act(float v, int dtype, int act)
 {
     switch (dtype) {
         case KO_F32:
             return v;
         case KO_F16:
             return ko_f16_to_f32(ko_f32_to_f16_rne(v));
-        default:
-            return ko_bf16_to_f32(ko_f32_to_bf16_trunc(v));
+        default: {
+            uint32_t u = ko_f32_to_bits(v);
+            if (act == KO_ACT_RELU && (u & 0x7fffffffu) >= 0x7f7f8000u && (u & 0x7fffffffu) < 0x7f800000u) {
+                u = (u & 0x80000000u) | 0x7f800000u;
+            }
+            return ko_bits_to_f32(u & 0xffff0000u);
+        }
     }
 }
 
@@ -300,14 +307,16 @@ static inline ko_pair ko_finish(const ko_desc *d, float acc, float alpha, float 
         t += beta * c_old;
     }
     float c1;
-    if (ct == KO_F16) {
+    if (ct == KO_F16 && (!have_bias || d->bias_dtype == KO_F16)) {
         /* hgemm writes fp16, the bias is then added in __fp16 (kudnn_gemm.cpp:189-192, :111) */
         c1 = ko_round_rne(t, KO_F16);
         if (have_bias) {
             c1 = ko_round_rne(c1 + bias, KO_F16);
         }
     } else {
-        /* fp32: plain add; bf16: add in fp32 then one RNE (kudnn_gemm.cpp:216-221) */
+        /* fp32: plain add; bf16: add in fp32 then one RNE (kudnn_gemm.cpp:216-221); fp16 result with a wider
+         * bias: no exact tuple exists, the product and the bias add run in fp32 and the result is rounded once
+         * (kudnn_gemm.cpp:679-692, and the W8A16 wrapper :348-360) */
         if (have_bias) {
             t += bias;
         }
@@ -315,7 +324,7 @@ static inline ko_pair ko_finish(const ko_desc *d, float acc, float alpha, float 
     }
     float c2 = c1;
     if (d->act != KO_ACT_NONE) {
-        c2 = ko_round_act(ko_activation(c1, d->act, d->act_alpha), ct);
+        c2 = ko_round_act(ko_activation(c1, d->act, d->act_alpha), ct, d->act);
     }
     ko_pair r;
     r.c = c2;
@@ -451,6 +460,11 @@ int ko_linear(const ko_desc *d, const void *a, const void *b, void *c, const voi
 #else
     (void)num_threads;
 #endif
+    if (d->a_dtype == KO_BF16 && d->b_dtype == KO_BF16 && d->c_dtype == KO_BF16 && !d->has_bias) {
+        /* the bias-free bf16 product is cblas_bgemm, which takes its two scalars as bf16 (kudnn_gemm.cpp:222-226) */
+        alpha = ko_bf16_to_f32(ko_f32_to_bf16_rne(alpha));
+        beta = ko_bf16_to_f32(ko_f32_to_bf16_rne(beta));
+    }
     const int64_t m = d->m, n = d->n, k = d->k;
     const int64_t kp = (k + KO_LANES - 1) / KO_LANES * KO_LANES;
     float *pa = (float *)aligned_alloc(64, (size_t)(m * kp) * sizeof(float));

@@ -3,7 +3,8 @@ library through its C ABI, and the comparison rules.
 
 A "case" is a plain dict:
     m, n, k            extents
-    dtype              "f32" | "f16" | "bf16"  (a, b, c, res, out; bias too unless bias_dtype is given)
+    dtype              "f32" | "f16" | "bf16"  (a, b; also c, res, out unless c_dtype is given; bias unless bias_dtype)
+    c_dtype            element type of c, res and out when it differs from the inputs' (f16 / bf16 inputs -> f32)
     bias               None | "row" ([1,n]) | "col" ([m,1]) | "scalar" ([1,1]) | "full" ([m,n])
     act, act_alpha     activation code (kudnn_b200.ACT_*) and its parameter
     res_op             kudnn_b200.RES_* ; gamma
@@ -27,7 +28,7 @@ DT = {"f32": kb.F32, "f16": kb.F16, "bf16": kb.BF16}
 def case_defaults(case):
     c = dict(dtype="bf16", bias=None, act=kb.ACT_NONE, act_alpha=1.0, res_op=kb.RES_NONE, gamma=1.0, a_layout="AB",
              b_layout="BA", x_dist="uniform", w_std=None, alpha=1.0, beta=0.0, batch=(), a_bcast=False, b_bcast=True,
-             seed=0, bias_dtype=None, want_c=True)
+             seed=0, bias_dtype=None, c_dtype=None, want_c=True)
     c.update(case)
     return c
 
@@ -73,6 +74,7 @@ def build_case(case):
         c0 = draw_x((nb, m, n))
 
     bias_code = DT[c["bias_dtype"]] if c["bias_dtype"] else code
+    c_code = DT[c["c_dtype"]] if c["c_dtype"] else code
     arrays = {}
     # a: [batch, m, k] logical; memory layout AB (k fastest) or BA (m fastest)
     if c["a_layout"] == "AB":
@@ -94,9 +96,9 @@ def build_case(case):
     else:
         bias_sm = bias_sn = 0
     if res is not None:
-        arrays["res"] = _storage(res, code)
+        arrays["res"] = _storage(res, c_code)
     if c0 is not None:
-        arrays["c0"] = _storage(c0, code)
+        arrays["c0"] = _storage(c0, c_code)
 
     def bstrides(per_matrix, broadcast):
         # contiguous batch strides for up to three leading dims, aligned to the right of batch[3]
@@ -113,7 +115,7 @@ def build_case(case):
     ext3 = tuple([0] * (3 - len(batch)) + list(batch)) if batch else (0, 0, 0)
     desc = kb.make_desc(
         m, n, k, code, a_strides=(a_sm, a_sk), b_strides=(b_sk, b_sn), has_bias=bias is not None,
-        bias_strides=(bias_sm, bias_sn), bias_dtype=bias_code, act=c["act"], act_alpha=c["act_alpha"],
+        bias_strides=(bias_sm, bias_sn), bias_dtype=bias_code, c_dtype=c_code, act=c["act"], act_alpha=c["act_alpha"],
         res_op=c["res_op"], batch=ext3, a_sb=bstrides(a_mat, c["a_bcast"]), b_sb=bstrides(b_mat, c["b_bcast"]),
         c_sb=bstrides(m * n, False), bias_sb=(0, 0, 0), res_sb=bstrides(m * n, False), out_sb=bstrides(m * n, False))
     return desc, arrays, c
@@ -216,6 +218,8 @@ def compare(got, ref, code):
     err = np.abs(g - r)
     scale = max(float(np.max(np.abs(r))), 1e-30)
     info = {"max_abs": float(err.max()), "normwise": float(err.max() / scale)}
+    # the per-element form with a floor of 1e-3 * max|ref|: reported beside the figure that is enforced
+    info["strict_fp32_rel"] = float(np.max(err / np.maximum(np.abs(r), 1e-3 * scale)))
     if code == kb.F32:
         assert info["normwise"] <= FP32_NORMWISE_TOL, "fp32 normwise error %.3e" % info["normwise"]
     else:
@@ -224,6 +228,8 @@ def compare(got, ref, code):
         ulp = np.abs(_ordered(got.view(np.uint16)) - _ordered(ref.view(np.uint16)))
         info["worst_over_bound"] = float(np.max(err / bound))
         info["over_bound_fraction"] = float(np.mean(over))
+        info["over_bound_count"] = int(np.count_nonzero(over))
+        info["elements"] = int(over.size)
         info["max_ulp"] = int(ulp.max())
         info["bit_exact_fraction"] = float(np.mean(ulp == 0))
         assert info["over_bound_fraction"] <= HALF_OUTLIER_FRACTION, \

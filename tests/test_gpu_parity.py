@@ -234,6 +234,70 @@ def test_tc_agrees_with_general_kernel(cuda_device):
     assert info["bit_exact_fraction"] > 0.99
 
 
+
+# The tensor-core kernel's epilogue comes in two forms: one with the activation and the element type fixed at compile
+# time (relu / swish / gelu_tanh, every tensor in the input type) and a general one that reads both from the
+# descriptor.  These cases take the general form on each launch shape: a single CTA per tile, CTA pairs, and the
+# cluster split-K whose last pass runs the chain from shared memory.
+TC_SHAPES = {"single": (260, 264, 128), "pair": (2560, 2048, 136), "splitk": (128, 1024, 1024)}
+TC_GENERAL = {
+    "gelu_erf": dict(dtype="bf16", bias="row", act=kb.ACT_GELU_ERF),
+    "sigmoid": dict(dtype="f16", bias="row", act=kb.ACT_SIGMOID, res_op=kb.RES_IDENTICAL),
+    "tanh": dict(dtype="bf16", bias="row", act=kb.ACT_TANH, res_op=kb.RES_EXT, gamma=0.5),
+    "gelu_erf_f32": dict(dtype="f32", bias="row", act=kb.ACT_GELU_ERF),
+    # the reference's <bf16, bf16, bf16, float> instance (kudnn_gemm.cpp:208-227): fp32 bias, bf16 everything else
+    "bf16_f32bias": dict(dtype="bf16", bias="row", bias_dtype="f32", act=kb.ACT_SWISH),
+    # <fp16, fp16, float, float> and <bf16, bf16, float, float> (kudnn_gemm.cpp:195-206, :229-241)
+    "f16_to_f32": dict(dtype="f16", c_dtype="f32", bias="row", bias_dtype="f32", act=kb.ACT_GELU_TANH,
+                       res_op=kb.RES_IDENTICAL),
+    "bf16_to_f32": dict(dtype="bf16", c_dtype="f32", bias="row", bias_dtype="f32", act=kb.ACT_RELU, act_alpha=0.0),
+    "bf16_to_f32_nobias": dict(dtype="bf16", c_dtype="f32"),
+    # fp16 result with an fp32 bias has no exact instance: product and bias add in fp32, one rounding
+    "f16_f32bias": dict(dtype="f16", bias="row", bias_dtype="f32", act=kb.ACT_SWISH, res_op=kb.RES_ELTWISE_MUL),
+}
+
+
+@pytest.mark.parametrize("shape", sorted(TC_SHAPES))
+@pytest.mark.parametrize("variant", sorted(TC_GENERAL))
+def test_tc_general_epilogue(cuda_device, shape, variant):
+    m, n, k = TC_SHAPES[shape]
+    case = dict(m=m, n=n, k=k, x_dist="normal", w_std=0.05, seed=53, **TC_GENERAL[variant])
+    info = helpers.parity(case, cuda_device, kernel=kb.KERNEL_TC, acc=ko.ACC_F64, expect_kernel=kb.KERNEL_TC)
+    print("tc general epilogue", shape, variant, info)
+
+
+@pytest.mark.parametrize("variant", ["bf16_f32bias", "f16_to_f32", "bf16_to_f32", "f16_f32bias"])
+@pytest.mark.parametrize("kernel,m", [(kb.KERNEL_SIMT, 67), (kb.KERNEL_GEMV_MMA, 7), (kb.KERNEL_GEMV_FMA, 2)])
+def test_mixed_type_tuples_other_kernels(cuda_device, variant, kernel, m):
+    case = dict(m=m, n=520, k=264, x_dist="normal", w_std=0.05, seed=54, **TC_GENERAL[variant])
+    helpers.parity(case, cuda_device, kernel=kernel, acc=ko.ACC_F64, expect_kernel=kernel)
+
+
+def test_bf16_scalars_of_the_bias_free_product(cuda_device):
+    # without a bias the reference multiplies bf16 operands with cblas_bgemm, whose alpha and beta are bf16
+    # (kudnn_gemm.cpp:222-226): 0.3 becomes 0.30078125
+    for kernel, m in ((kb.KERNEL_TC, 256), (kb.KERNEL_SIMT, 50)):
+        case = dict(m=m, n=256, k=256, dtype="bf16", alpha=0.3, beta=0.7, w_std=0.05, seed=55)
+        helpers.parity(case, cuda_device, kernel=kernel, acc=ko.ACC_F64, expect_kernel=kernel)
+
+
+def test_relu_bf16_overflow_rounds_to_infinity(cuda_device):
+    # relu with a negative slope on a huge negative bf16 value: the product lies between the largest bf16 and
+    # infinity, and the reference stores infinity instead of truncating (vml_sve_base.h:97-109)
+    m, n, k = 128, 256, 64
+    a = np.zeros((m, k), dtype=np.float32)
+    b = np.zeros((n, k), dtype=np.float32)
+    a[:, 0] = -1.0
+    b[:, 0] = 3.3895313892515355e38  # 0x7f7f0000, the largest finite bf16
+    desc = kb.make_desc(m, n, k, kb.BF16, act=kb.ACT_RELU, act_alpha=-1.0029296875)
+    arrays = {"a": ko.to_storage(a, kb.BF16), "b": ko.to_storage(b, kb.BF16)}
+    c = helpers.case_defaults(dict(m=m, n=n, k=k))
+    ref_c, _ = helpers.run_oracle(desc, arrays, c)
+    assert np.all(ref_c == 0x7f80)
+    for kernel in (kb.KERNEL_TC, kb.KERNEL_SIMT):
+        got_c, _, used = helpers.run_gpu(desc, arrays, c, cuda_device, kernel=kernel)
+        assert used == kernel and np.array_equal(got_c.reshape(m, n), ref_c.reshape(m, n))
+
 # ------------------------------------------------------------------------------------------- golden vectors, host path
 
 def _golden_names():
@@ -329,7 +393,7 @@ def test_config1_fp32_relu_full(cuda_device):
     case = dict(m=128, n=1024, k=1024, dtype="f32", bias="row", act=kb.ACT_RELU, act_alpha=0.0, x_dist="uniform",
                 w_std=0.02, seed=0)
     info = helpers.parity(case, cuda_device, acc=ko.ACC_F64, expect_kernel=kb.KERNEL_TC)
-    print("config 1 normwise error vs fp64 oracle:", info["c"]["normwise"])
+    print("config 1 vs fp64 oracle:", info["c"])
 
 
 def test_config2_bf16_silu_full(cuda_device):
@@ -343,6 +407,7 @@ def test_config2_bf16_silu_full(cuda_device):
     lin.check(stream=torch.cuda.current_stream().cuda_stream)
     assert lin.last_kernel == kb.KERNEL_TC
     info = _check_rows(desc, x, w, bias, None, y, None, _sample_rows(m, 96, 1))
+    print("config 2:", info["c"])
     assert info["c"]["bit_exact_fraction"] > 0.98
 
 
@@ -355,7 +420,8 @@ def test_config3_fp16_gelu_residual_full(cuda_device):
     lin.run(x, w, None, bias, res, out, stream=torch.cuda.current_stream().cuda_stream)
     lin.check(stream=torch.cuda.current_stream().cuda_stream)
     assert lin.last_kernel == kb.KERNEL_TC
-    _check_rows(desc, x, w, bias, res, None, out, _sample_rows(m, 96, 2))
+    info = _check_rows(desc, x, w, bias, res, None, out, _sample_rows(m, 96, 2))
+    print("config 3:", info["out"])
 
 
 @pytest.mark.parametrize("m", [1, 4, 16])
@@ -369,6 +435,7 @@ def test_config4_decode_gate_full(cuda_device, m):
     lin.check(stream=torch.cuda.current_stream().cuda_stream)
     assert lin.last_kernel in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA)
     info = _check_rows(desc, x, w, None, gate, None, out, list(range(m)))
+    print("config 4, m = %d:" % m, info["out"])
     assert info["out"]["bit_exact_fraction"] > 0.98
 
 
@@ -395,6 +462,33 @@ def test_config5_sharded_rows_full(cuda_device):
     lh.run(x[half:], w, y2[half:], bias, stream=stream)
     lh.check(stream=stream)
     assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+
+
+def test_config5_full_size_one_gpu(cuda_device):
+    """The whole 32768-row layer on one GPU (2.9 GB of operands): the oracle on sampled rows, among them both sides of
+    the first tile boundaries and the last row of the last tile, and the size-independent linearity property."""
+    m, n, k = 32768, 28672, 8192
+    x, w, bias, _ = _device_inputs(m, n, k, "bf16", cuda_device, 0)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=cuda_device)
+    desc = kb.make_desc(m, n, k, kb.BF16, has_bias=True, act=kb.ACT_SWISH)
+    lin = kb.Linear(desc)
+    stream = torch.cuda.current_stream().cuda_stream
+    lin.run(x, w, y, bias, stream=stream)
+    lin.check(stream=stream)
+    assert lin.last_kernel == kb.KERNEL_TC
+    rows = sorted(set(_sample_rows(m, 24, 7)) | {127, 128, 255, 256, 257, m - 256, m - 129, m - 128, m - 1})
+    info = _check_rows(desc, x, w, bias, None, y, None, rows)
+    print("config 5, 32768 rows on one GPU:", info["c"])
+    assert info["c"]["bit_exact_fraction"] > 0.98
+    del y
+    # no activation, fp32 result: the column sums of x . W^T equal (sum of the rows of x) . W^T
+    y32 = torch.empty(m, n, dtype=torch.float32, device=cuda_device)
+    lin2 = kb.Linear(kb.make_desc(m, n, k, kb.BF16, c_dtype=kb.F32))
+    lin2.run(x, w, y32, stream=stream)
+    lin2.check(stream=stream)
+    col_sums = y32.sum(dim=0, dtype=torch.float64).cpu().numpy()
+    want = w.double().cpu().numpy() @ x.sum(dim=0, dtype=torch.float64).cpu().numpy()
+    assert np.max(np.abs(col_sums - want)) <= 2e-5 * np.abs(want).max()
 
 
 def test_row_sum_property_full_size(cuda_device):

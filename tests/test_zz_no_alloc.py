@@ -3,9 +3,10 @@
 It serves callers that cannot call cudaMalloc at the moment they need a decode-shaped Linear: engines that gave all
 of HBM to their own pools at start-up, and plug-ins whose host forbids allocation inside an operator call.  Its
 split-K scratch is one fixed array per device that every call shares and that keeps the previous call's contents,
-so the check that matters is that two calls in a row, on problems of different sizes, each reproduce what the
-regular (allocating) entry point computes.  This file sorts last on purpose: when a run stops at the first failure,
-every other test has already run.
+so the checks that matter are that two calls in a row, on problems of different sizes, each reproduce what the
+regular (allocating) entry point and the CPU oracle compute, and that a call, once its kernel variant has been
+loaded, leaves the amount of free device memory unchanged.  This file sorts last on purpose: when a run stops at
+the first failure, every other test has already run.
 """
 import numpy as np
 import pytest
@@ -40,6 +41,11 @@ def _both_ways(case, device):
     helpers.compare(helpers._from_torch(got_c), helpers._from_torch(ref_c), desc.c_dtype)
     if has_res:
         helpers.compare(helpers._from_torch(got_o), helpers._from_torch(ref_o), desc.out_dtype)
+    # and against the CPU oracle, not only against the library's other entry point
+    ora_c, ora_o = helpers.run_oracle(desc, arrays, c)
+    helpers.compare(helpers._from_torch(got_c).reshape(ora_c.shape), ora_c, desc.c_dtype)
+    if has_res:
+        helpers.compare(helpers._from_torch(got_o).reshape(ora_o.shape), ora_o, desc.out_dtype)
 
 
 def test_two_calls_in_a_row_match_the_allocating_entry_point(cuda_device):
@@ -49,6 +55,29 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(cuda_device):
     _both_ways(first, cuda_device)
     _both_ways(second, cuda_device)
     _both_ways(first, cuda_device)
+
+
+def test_later_calls_take_no_device_memory(cuda_device):
+    """What the entry point exists for.  The first call on a device creates the scratch array and loads the kernel
+    variant it launches (the CUDA runtime loads device code lazily), which takes memory from the driver once; every
+    later call of that variant must leave the free device memory exactly as it found it."""
+    case = dict(m=16, n=3000, k=4096, dtype="bf16", res_op=kb.RES_ELTWISE_MUL, x_dist="normal", w_std=0.02, seed=64)
+    desc, arrays, c = helpers.build_case(case)
+    d = {k: helpers._to_torch(v, cuda_device) for k, v in arrays.items()}
+    smaller = kb.make_desc(16, 2000, 4096, kb.BF16, res_op=kb.RES_ELTWISE_MUL)  # same variant, cut differently
+    out = torch.zeros((16, 3000), dtype=torch.int16, device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+    kb.run_static_scratch(desc, d["a"], d["b"], None, None, d["res"], out, stream=stream)  # warm-up: loads the variant
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for i in range(6):
+        kb.run_static_scratch(desc if i % 2 == 0 else smaller, d["a"], d["b"], None, None, d["res"], out, stream=stream)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    kb.run_static_scratch(desc, d["a"], d["b"], None, None, d["res"], out, stream=stream)
+    torch.cuda.synchronize()
+    _, ref_o = helpers.run_oracle(desc, arrays, c)
+    helpers.compare(helpers._from_torch(out).reshape(ref_o.shape), ref_o, desc.out_dtype)
 
 
 def test_single_row_fp32(cuda_device):

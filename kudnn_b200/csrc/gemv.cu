@@ -44,6 +44,14 @@ struct GemvParams {
     int slots;         // slots per unit per chunk
     float *partials;
     unsigned int *counters;
+    // Decode-packed weights, when the handle holds them: groups of 8 rows, each cut into blocks of 64 k; a block is
+    // 1 KiB of contiguous memory, zero padded to 8 rows and to blk_kb * 64 columns.  Inside a block the 16-byte chunk
+    // c (k = 8c .. 8c+7) of row r sits at byte (c & 1) * 512 + (4 r + c / 2) * 16: lane 4 r + t of a warp finds the
+    // two chunks 2t and 2t+1 it feeds to the tensor cores at the same place in the two halves, so every load
+    // instruction of a warp reads 512 consecutive bytes instead of 8 pieces that lie a weight row apart, which HBM
+    // serves a few percent faster.  The MMA kernels read this copy; the FMA kernel reads the plain K-major rows.
+    const unsigned short *w_blk;
+    int blk_kb;  // 64-k blocks per group
     EpiParams epi;
 };
 
@@ -353,7 +361,14 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_mma_kernel(const Ge
 #pragma unroll
                 for (int h = 0; h < (kWide ? 2 : 1); ++h) {
                     wv[u][h] = make_uint4(0u, 0u, 0u, 0u);
-                    if (i + u < nb && row_ok && (kc0 + kloc + tig * (kLaneBytes / 2) + h * 8) < p.k) {
+                    if (p.w_blk != nullptr) {
+                        const int k_abs = kc0 + kloc + tig * (kLaneBytes / 2) + h * 8;
+                        if (i + u < nb && (k_abs >> 6) < p.blk_kb) {
+                            const int c = (k_abs & 63) >> 3;
+                            wv[u][h] = ld_stream_16(p.w_blk + (group * p.blk_kb + (k_abs >> 6)) * 512 + (c & 1) * 256 +
+                                                    (gid * 4 + (c >> 1)) * 8);
+                        }
+                    } else if (i + u < nb && row_ok && (kc0 + kloc + tig * (kLaneBytes / 2) + h * 8) < p.k) {
                         wv[u][h] = ld_stream_16(wrow + kloc + h * 8);
                     }
                 }
@@ -427,6 +442,20 @@ __global__ void __launch_bounds__(kStagedThreads, 1) gemv_mma_staged_kernel(cons
     // rows [row0, row0 + rows_ok) of the weights, block blk of this chunk: one 512-byte row segment per instruction
     auto load_block = [&](uint4 (&v)[8], long long row0, int rows_ok, int blk) {
         const int kloc = blk * kStagedBlockK;
+        if (p.w_blk != nullptr) {
+            // the block is 4 KiB of contiguous memory (four 64-k blocks of this group): instruction i reads bytes
+            // [512 i, 512 i + 512), i.e. 64-k block i / 2, row lane / 4, 16-byte chunk 2 (lane % 4) + i % 2
+            const int kb64 = (kc0 + kloc) >> 6;
+            const unsigned short *src = p.w_blk + ((row0 >> 3) * p.blk_kb + kb64) * 512 + lane * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (kb64 + (i >> 1) < p.blk_kb) {
+                    v[i] = ld_stream_16(src + i * 256);
+                }
+            }
+            return;
+        }
         const bool k_ok = kc0 + kloc + lane * 8 < k_end;
         const unsigned short *src = wg + row0 * p.w_ld + kc0 + kloc + lane * 8;
 #pragma unroll
@@ -513,6 +542,9 @@ __global__ void __launch_bounds__(kStagedThreads, 1) gemv_mma_staged_kernel(cons
     const unsigned char *xb_row = smem_raw + (gid + 8) * row_bytes + tig * 16;
     unsigned char *stage = smem_raw + kRows * row_bytes + warp_in_cta * kStagedWarpBytes;
     const uint32_t stage_st = static_cast<uint32_t>(__cvta_generic_to_shared(stage)) + static_cast<uint32_t>(lane * 16);
+    // decode-packed weights: where register i of load_block goes in the staged [8 rows][256 k] block
+    const uint32_t stage_st_blk = static_cast<uint32_t>(__cvta_generic_to_shared(stage)) +
+                                  static_cast<uint32_t>((lane >> 2) * kStagedPitch + (lane & 3) * 32);
     const uint32_t stage_ld = static_cast<uint32_t>(__cvta_generic_to_shared(stage)) +
                               static_cast<uint32_t>((lane & 7) * kStagedPitch + (lane >> 3) * 16);
     bool preloaded = true;
@@ -529,8 +561,10 @@ __global__ void __launch_bounds__(kStagedThreads, 1) gemv_mma_staged_kernel(cons
             __syncwarp();  // the ldmatrix reads of the previous block are done
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_st + r * kStagedPitch), "r"(v[r].x),
-                             "r"(v[r].y), "r"(v[r].z), "r"(v[r].w)
+                const uint32_t dst = (p.w_blk != nullptr) ? stage_st_blk + (r & 1) * 16 + (r >> 1) * 128
+                                                          : stage_st + r * kStagedPitch;
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[r].x), "r"(v[r].y), "r"(v[r].z),
+                             "r"(v[r].w)
                              : "memory");
             }
             __syncwarp();
@@ -708,11 +742,10 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     const size_t max_smem = 200 * 1024;
     int kernel = forced_kernel;
     if (kernel != KUDNN_B200_KERNEL_GEMV_FMA && kernel != KUDNN_B200_KERNEL_GEMV_MMA) {
-        const int fma_max_m = env_int("KUDNN_B200_GEMV_FMA_MAX_M", 1);
-        kernel = (dt == KUDNN_B200_F32 || pr.m <= fma_max_m) ? KUDNN_B200_KERNEL_GEMV_FMA : KUDNN_B200_KERNEL_GEMV_MMA;
+        kernel = (dt == KUDNN_B200_F32 || pr.m <= 1) ? KUDNN_B200_KERNEL_GEMV_FMA : KUDNN_B200_KERNEL_GEMV_MMA;
     }
     plan->kernel = kernel;
-    int shape = env_int("KUDNN_B200_GEMV_SHAPE", -1);
+    int shape = -1;
     if (kernel == KUDNN_B200_KERNEL_GEMV_FMA) {
         if (pr.m > 4) {
             return false;
@@ -754,17 +787,20 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
         return false;
     }
     const int rows = pr.m > 8 ? 16 : 8;
-    // The staged feed wins for up to 8 activation rows; with 16 rows the second half of the activation operand
-    // doubles the shared-memory reads per block and the fragment-shaped loads are faster (measured).  The
-    // environment switch forces one feed for every m (1) or turns the staged feed off (0).
+    // Which feed (measured on config 4, microseconds per call).  Up to 8 activation rows: 88 for the staged feed on
+    // decode-packed weights and for the fragment-shaped loads on plain rows, 92-94 for the other two pairings.  With
+    // 16 rows the second half of the activation operand doubles the shared-memory reads per staged block (107
+    // against 90 for the fragment-shaped loads of 32 bytes per lane).  The environment switches exist for the tests,
+    // which run every feed on every shape: KUDNN_B200_GEMV_STAGED forces the staged feed for every m (1) or turns it
+    // off (0), KUDNN_B200_GEMV_WIDE=0 makes the fragment-shaped loads 16 bytes per lane.
     const int staged_env = env_int("KUDNN_B200_GEMV_STAGED", -1);
-    const bool staged = staged_env < 0 ? rows == 8 : staged_env != 0;
+    const bool staged = staged_env < 0 ? (rows == 8 && pr.b_blocked != nullptr) : staged_env != 0;
     if (staged && (shape < 0 || shape == kStagedShape)) {
         // staged feed: 512 threads, one CTA per SM, blocks of 8 rows x 256 k
         const int warps = kStagedThreads / 32;
         const size_t staging = static_cast<size_t>(warps) * kStagedWarpBytes;
         const size_t budget = 225 * 1024 - staging;
-        int ksplit = env_int("KUDNN_B200_GEMV_KSPLIT", 0);
+        int ksplit = 0;
         auto chunk_len = [&](int parts) {
             return ((pr.k + parts - 1) / parts + kStagedBlockK - 1) / kStagedBlockK * kStagedBlockK;
         };
@@ -804,7 +840,7 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
         shape = (rows == 16) ? 1 : 0;
     }
     const size_t smem_budget = (kShapes[shape].min_blocks == 2) ? 100 * 1024 : max_smem;
-    int ksplit = env_int("KUDNN_B200_GEMV_KSPLIT", 0);
+    int ksplit = 0;
     // 16 activation rows: blocks of 64 k with 32 bytes per lane (see gemv_mma_kernel)
     const bool wide = rows == 16 && env_int("KUDNN_B200_GEMV_WIDE", 1) != 0;
     const long long block_k = wide ? 64 : 32;
@@ -870,8 +906,10 @@ cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const Gem
     p.partials = ws.partials;
     p.counters = ws.counters;
     p.epi = pr.epi;
+    p.w_blk = plan.kernel == KUDNN_B200_KERNEL_GEMV_MMA ? static_cast<const unsigned short *>(pr.b_blocked) : nullptr;
+    p.blk_kb = static_cast<int>(pr.b_blocked_kpad / 64);
     const int dt = pr.a_dtype;
-    const int unroll = env_int("KUDNN_B200_GEMV_UNROLL", 4);
+    const int unroll = 4;
     if (plan.kernel == KUDNN_B200_KERNEL_GEMV_FMA) {
         const int vec = (dt == KUDNN_B200_F32) ? 4 : 8;
         p.kb = static_cast<int>((pr.k + 32 * vec - 1) / (32 * vec));

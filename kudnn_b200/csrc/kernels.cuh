@@ -12,6 +12,9 @@ struct LinearProblem {
     long long m, n, k;
     long long a_sm, a_sk, b_sk, b_sn;
     int a_dtype, b_dtype;
+    // the weights once more in the decode-packed layout (see GemvParams::w_blk in gemv.cu), or null
+    const void *b_blocked = nullptr;
+    long long b_blocked_kpad = 0;
     EpiParams epi;
     BatchParams batch;
     long long batch_count;
@@ -70,6 +73,10 @@ struct TcPlan {
 };
 bool tc_available();
 const char *tc_unavailable_reason();
+// Tensor map (written into 128 bytes at map128) of a K-major matrix [rows, k_total] with row pitch ld_elems, for TMA
+// boxes of 128 bytes of K x box_rows rows with the 128-byte swizzle; rows and columns out of range read as zero.
+cudaError_t tc_encode_kmajor(void *map128, const void *base, int kind, long long rows, long long k_total, long long ld_elems,
+                             int box_rows);
 // with_staging: the launch writes output mirrors and needs the epilogue's row staging in shared memory
 cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm_count, bool with_staging, TcPlan *plan);
 // wait_limit_cycles: SM cycles after which a device-side wait gives up (0 = the default of about two seconds);
@@ -81,6 +88,10 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
 // dst[r, kk] (row pitch ldd, K-major) = src[r*s_row + kk*s_k] converted to dst_dtype; columns [k, k_pad) are zeroed.
 cudaError_t launch_pack_kmajor(const void *src, int src_dtype, long long rows, long long k, long long s_row,
                                long long s_k, void *dst, int dst_dtype, long long ldd, long long k_pad,
+                               cudaStream_t stream);
+// 16-bit K-major rows (pitch ld elements) -> the decode-packed layout: [ceil(rows / 8)][k_pad / 64] blocks of 1 KiB
+// (8 rows x 64 k, chunk order as described at GemvParams::w_blk), zero padded.
+cudaError_t launch_pack_blocks(const void *src, long long rows, long long k, long long ld, void *dst, long long k_pad,
                                cudaStream_t stream);
 // fp32 -> three K-major TF32 planes side by side at the start of each dst row (row pitch ldd floats).  With
 // hi = tf32(x) and lo = tf32(x - hi), activations are laid out [lo | hi | hi] and weights [hi | lo | hi], so that one

@@ -139,6 +139,7 @@ struct kudnn_b200_linear_s {
     DeviceBuffer a_scratch;     // per-call packed activations
     DeviceBuffer b_scratch;     // per-call packed weights (when not pre-packed)
     DeviceBuffer b_packed;      // pre-packed weights
+    DeviceBuffer b_blocked;     // decode-shaped handles: the weights once more in 8-row x 64-k blocks
     DeviceBuffer stage[6];      // host-pointer staging: a, b, c, bias, res, out
 
     // pre-pack state
@@ -147,6 +148,7 @@ struct kudnn_b200_linear_s {
                                        // pointer when that already is K-major); fp32: the three TF32 planes
     const void *packed_raw = nullptr;  // K-major copy in the original element type (what the other kernels read)
     long long packed_ld = 0, packed_ktotal = 0;
+    long long blocked_kpad = 0;  // columns per row of b_blocked (k rounded up to 256); 0 = no blocked copy
 
     // tensor-map cache of the last tensor-core launch
     kb::TcPlan tc_plan;
@@ -427,6 +429,10 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
         pr.b = h->packed_raw;
         pr.b_sk = 1;
         pr.b_sn = h->packed_ld;
+        if (h->blocked_kpad > 0) {
+            pr.b_blocked = h->b_blocked.ptr;
+            pr.b_blocked_kpad = h->blocked_kpad;
+        }
     }
 
     // ---- streaming kernels (m <= 16)
@@ -891,6 +897,7 @@ int kudnn_b200_linear_destroy(kudnn_b200_linear_t h)
         h->a_scratch.release();
         h->b_scratch.release();
         h->b_packed.release();
+        h->b_blocked.release();
         for (auto &s : h->stage) {
             s.release();
         }
@@ -967,6 +974,24 @@ int kudnn_b200_linear_prepack(kudnn_b200_linear_t h, const void *b, void *cuda_s
         h->packed_raw = raw;
         h->packed_ld = ld;
         h->packed_ktotal = kt;
+    }
+    // Decode-shaped primitives (m <= 16, 16-bit types) stream the whole weight matrix on every call: they get a
+    // second copy in blocks of 8 rows x 64 k, the unit their MMA kernels read, so that a warp's loads are one
+    // contiguous piece of memory.  A single activation row stays on the FMA kernel, which reads plain rows.
+    h->blocked_kpad = 0;
+    if (d.m >= 2 && d.m <= 16 && d.b_dtype != KUDNN_B200_F32 && d.a_dtype == d.b_dtype && d.k % 8 == 0) {
+        const long long k_pad = round_up(d.k, 256);
+        e = h->b_blocked.reserve(static_cast<size_t>(round_up(d.n, 8)) * k_pad * 2);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "decode-packed weights");
+        }
+        e = kb::launch_pack_blocks(h->packed_raw, d.n, d.k, h->packed_ld, h->b_blocked.ptr, k_pad, stream);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "decode pack kernel");
+        }
+        h->blocked_kpad = k_pad;
+    } else {
+        h->b_blocked.release();
     }
     h->packed_key = b;
     // one-time cost: later runs may use other streams (the host-pointer pipeline does) and the staging buffer is reused
@@ -1143,9 +1168,11 @@ int kudnn_b200_linear_unpack(kudnn_b200_linear_t h)
     h->packed_ptr = nullptr;
     h->packed_raw = nullptr;
     h->packed_ld = h->packed_ktotal = 0;
+    h->blocked_kpad = 0;
     h->plan_valid = false;
     if (h->device >= 0) {
         h->b_packed.release();
+        h->b_blocked.release();
     }
     return KUDNN_B200_OK;
 }
@@ -1183,7 +1210,7 @@ int64_t kudnn_b200_linear_workspace_bytes(kudnn_b200_linear_t h)
         return 0;
     }
     return static_cast<int64_t>(h->gemv_partials.bytes + h->gemv_counters.bytes + h->a_scratch.bytes + h->b_scratch.bytes +
-                                h->b_packed.bytes);
+                                h->b_packed.bytes + h->b_blocked.bytes);
 }
 
 int kudnn_b200_shard_range(int64_t total, int nparts, int part, int64_t align, int64_t *begin, int64_t *count)

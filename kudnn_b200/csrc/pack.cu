@@ -103,7 +103,42 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float *src, long 
     }
 }
 
+// one thread per 16-byte chunk of the destination
+__global__ void __launch_bounds__(256) pack_blocks_kernel(const unsigned short *src, long long rows, long long k, long long ld,
+                                                          uint4 *dst, long long nkb, long long total_chunks)
+{
+    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (idx >= total_chunks) {
+        return;
+    }
+    // position in the block -> (row, 16-byte chunk): byte (c & 1) * 512 + (4 r + c / 2) * 16 holds chunk c of row r
+    const int pos = static_cast<int>(idx & 63);
+    const int r = (pos & 31) >> 2, c = (pos & 3) * 2 + (pos >> 5);
+    const long long blk = idx >> 6;
+    const long long kb = blk % nkb, g = blk / nkb;
+    const long long row = g * 8 + r, kk = kb * 64 + c * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows && kk < k) {  // k is a multiple of 8: a chunk is inside the row or outside of it
+        v = *reinterpret_cast<const uint4 *>(src + row * ld + kk);
+    }
+    dst[idx] = v;
+}
+
 }  // namespace
+
+cudaError_t launch_pack_blocks(const void *src, long long rows, long long k, long long ld, void *dst, long long k_pad,
+                               cudaStream_t stream)
+{
+    const long long nkb = k_pad / 64;
+    const long long total = (rows + 7) / 8 * nkb * 64;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffll) {
+        return cudaErrorInvalidValue;
+    }
+    pack_blocks_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const unsigned short *>(src), rows, k, ld,
+                                                                          static_cast<uint4 *>(dst), nkb, total);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_pack_kmajor(const void *src, int src_dtype, long long rows, long long k, long long s_row,
                                long long s_k, void *dst, int dst_dtype, long long ldd, long long k_pad,

@@ -114,6 +114,29 @@ def test_gemv_mma_sixteen_rows_shapes(cuda_device, monkeypatch, wide, n, k):
     helpers.parity(case, cuda_device, kernel=kb.KERNEL_GEMV_MMA, expect_kernel=kb.KERNEL_GEMV_MMA)
 
 
+@pytest.mark.parametrize("staged,wide", [(None, None), ("1", "1"), ("0", "1"), ("0", "0")])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m", [2, 4, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(1003, 1048), (300, 8192), (2600, 16384), (8, 8), (4000, 72)])
+def test_gemv_mma_decode_packed_weights(cuda_device, monkeypatch, staged, wide, dtype, m, n, k):
+    """Pre-packing a decode-shaped primitive stores the weights once more in blocks of 8 rows x 64 k, which is what
+    the MMA streaming kernels then read (every feed variant); results must not change."""
+    if staged is not None:
+        monkeypatch.setenv("KUDNN_B200_GEMV_STAGED", staged)
+        monkeypatch.setenv("KUDNN_B200_GEMV_WIDE", wide)
+    case = dict(m=m, n=n, k=k, dtype=dtype, bias="row", act=kb.ACT_SWISH, res_op=kb.RES_ELTWISE_MUL, x_dist="normal",
+                w_std=0.03, seed=40)
+    desc, arrays, c = helpers.build_case(case)
+    ref_c, ref_o = helpers.run_oracle(desc, arrays, c)
+    packed = helpers.run_gpu(desc, arrays, c, cuda_device, kernel=kb.KERNEL_GEMV_MMA, prepack=True)
+    plain = helpers.run_gpu(desc, arrays, c, cuda_device, kernel=kb.KERNEL_GEMV_MMA)
+    assert packed[2] == kb.KERNEL_GEMV_MMA
+    helpers.compare(packed[0], ref_c, desc.c_dtype)
+    helpers.compare(packed[1], ref_o, desc.out_dtype)
+    # same arithmetic in the same order, only the addresses differ
+    assert np.array_equal(packed[0], plain[0]) and np.array_equal(packed[1], plain[1])
+
+
 @pytest.mark.parametrize("m", [4, 16])
 def test_decode_default_is_deterministic(cuda_device, m):
     case = dict(m=m, n=4096, k=4096, dtype="bf16", res_op=kb.RES_ELTWISE_MUL, x_dist="normal", w_std=0.02, seed=36)
@@ -433,7 +456,7 @@ def test_config4_decode_gate_full(cuda_device, m):
     lin = kb.Linear(desc)
     lin.run(x, w, None, None, gate, out, stream=torch.cuda.current_stream().cuda_stream)
     lin.check(stream=torch.cuda.current_stream().cuda_stream)
-    assert lin.last_kernel in (kb.KERNEL_GEMV_FMA, kb.KERNEL_GEMV_MMA)
+    assert lin.last_kernel == (kb.KERNEL_GEMV_FMA if m == 1 else kb.KERNEL_GEMV_MMA)
     info = _check_rows(desc, x, w, None, gate, None, out, list(range(m)))
     print("config 4, m = %d:" % m, info["out"])
     assert info["out"]["bit_exact_fraction"] > 0.98

@@ -1358,8 +1358,13 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     if (tiles > (1ll << 30)) {
         return cudaErrorInvalidValue;
     }
-    // CTA pairs for the large-problem shape (256-wide tiles): 256 x 256 tiles over clusters of two
-    bool pair = bn == 256 && m > kBM;
+    // CTA pairs for the large-problem shape (256-wide tiles): 256 x 256 tiles over clusters of two.  Not for launches
+    // that run for many milliseconds: those are limited by the board's power cap, and the pair shape, which needs
+    // fewer cycles, draws enough more power per cycle to end up slower there (bf16 n = 28672, k = 8192, ms per call,
+    // pair / single CTA: 4096 rows 1.385 / 1.396, 8192 rows 2.84 / 2.85, 16384 rows 6.10 / 5.96, 32768 rows
+    // 13.3 / 12.4).
+    const double flops = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(ops.k_total);
+    bool pair = bn == 256 && m > kBM && flops < 6.0e12;
     if (const char *env = std::getenv("KUDNN_B200_TC_PAIR")) {
         pair = pair && std::atoi(env) != 0;
     }

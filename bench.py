@@ -440,6 +440,7 @@ def main():
     if world == 1 and not args.no_extras and wname == "c5m":
         early["configs"] = other_configs_leg(torch, kb, device, peaks, flush)
         early["decode_gemv"] = gemv_leg(torch, kb, device, peaks, flush)
+        early["eltwise"] = eltwise_leg(torch, kb, device, peaks, flush)
         torch.cuda.synchronize()
         time.sleep(1.0)
 
@@ -671,6 +672,33 @@ def other_configs_leg(torch, kb, device, peaks, flush):
             out[name]["note"] = "latency-bound: 0.27 GFLOP and 5.2 MB per call"
         del x, wt, bias, res, y, lin
         torch.cuda.empty_cache()
+    return out
+
+
+def eltwise_leg(torch, kb, device, peaks, flush):
+    """The operators either side of Linear, stand-alone: SiLU over the output of configuration 2 and RMS normalisation
+    (with scale) over the input of configuration 3.  Algorithmic bytes = every element read once and written once."""
+    out = {}
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=device).manual_seed(0)
+    m, n = 4096, 11008
+    x = torch.randn(m, n, generator=g, device=device).to(torch.bfloat16)
+    y = torch.empty_like(x)
+    ms = timed_steps(torch, lambda: kb.activation(x, y, m * n, kb.BF16, kb.BF16, kb.ACT_SWISH, 1.0, stream=stream), 30, 5, flush)
+    ms.sort()
+    gbs = 2.0 * m * n * 2 / (ms[len(ms) // 2] * 1e-3) / 1e9
+    out["activation_silu_bf16_4096x11008"] = {"us": ms[len(ms) // 2] * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                              "algorithmic_bytes": 2 * m * n * 2}
+    rows, axis = 8192, 4096
+    x = torch.randn(rows, axis, generator=g, device=device).to(torch.float16)
+    scale = torch.randn(axis, generator=g, device=device).to(torch.float16)
+    y = torch.empty_like(x)
+    ms = timed_steps(torch, lambda: kb.rmsnorm(x, y, rows, axis, kb.F16, scale=scale, flags=kb.NORM_USE_SCALE, eps=1e-5,
+                                               stream=stream), 30, 5, flush)
+    ms.sort()
+    gbs = (2.0 * rows * axis + axis) * 2 / (ms[len(ms) // 2] * 1e-3) / 1e9
+    out["rmsnorm_f16_8192x4096"] = {"us": ms[len(ms) // 2] * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                    "algorithmic_bytes": (2 * rows * axis + axis) * 2}
     return out
 
 

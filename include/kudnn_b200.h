@@ -162,6 +162,32 @@ KUDNN_B200_API int kudnn_b200_linear_run_any(kudnn_b200_linear_t handle, const k
 KUDNN_B200_API int kudnn_b200_linear_run_static_scratch(const kudnn_b200_linear_desc *desc,
                                                         const kudnn_b200_linear_args *args, void *cuda_stream);
 
+/* ---- the operators either side of Linear ---------------------------------------------------------------------------
+ * Stand-alone activation pass over `count` elements of a dense tensor.  Replaces ActivationLayerFWD::Run
+ * (src/dnn/include/operations/kudnn_eltwise.hpp:62-76, src/dnn/src/kudnn_eltwise.cpp:500-586): fp32 arithmetic; with
+ * equal source and result types fp16 results are rounded to nearest even and bf16 results truncated, otherwise the
+ * result is rounded once from fp32.  `act` is one of the KUDNN_B200_ACT_* codes (RELU, TANH, SIGMOID, GELU_TANH, SWISH,
+ * GELU_ERF; the reference's other 16 functions return UNSUPPORTED), alpha the relu slope / swish factor.  src and dst
+ * are both device memory (16-byte aligned; asynchronous on the stream) or both host memory (staged; synchronous). */
+KUDNN_B200_API int kudnn_b200_activation_validate(int64_t count, int src_dtype, int dst_dtype, int act);
+KUDNN_B200_API int kudnn_b200_activation_run(const void *src, void *dst, int64_t count, int src_dtype, int dst_dtype,
+                                             int act, float alpha, void *cuda_stream);
+
+/* RMS normalisation over the last axis of a dense [rows, axis] tensor: y = x * (scale * 1 / sqrt(variance + eps)),
+ * variance = mean(x^2) per row in fp32, or the caller's `variance` with USE_GLOBAL_STATS; with save_stats the computed
+ * variances are written to `variance`.  Replaces RMSNormalizationLayerFWD::Run
+ * (src/dnn/include/operations/kudnn_rms_normalization.hpp:26-44, kernels/rmsnorm/kudnn_rmsnorm_fwd_last_def.hpp:128-180).
+ * Flags are KuDNN::NormalizationFlags (src/dnn/include/types/kudnn_normalization.hpp:18-24).  The reference accepts
+ * fp16 only; bf16 and fp32 are accepted here as well.  Device or host pointers, as for the activation. */
+#define KUDNN_B200_NORM_USE_GLOBAL_STATS 0x1
+#define KUDNN_B200_NORM_USE_SCALE 0x2
+#define KUDNN_B200_NORM_USE_SHIFT 0x4
+#define KUDNN_B200_NORM_FUSE_RELU 0x8
+KUDNN_B200_API int kudnn_b200_rmsnorm_validate(int64_t rows, int64_t axis, int dtype, int flags);
+KUDNN_B200_API int kudnn_b200_rmsnorm_run(const void *src, void *dst, const void *scale, float *variance, int64_t rows,
+                                          int64_t axis, int dtype, int flags, int save_stats, float eps,
+                                          void *cuda_stream);
+
 /* Reads the device-side status word of the handle (bounded waits that gave up) after synchronising the stream. */
 KUDNN_B200_API int kudnn_b200_linear_check(kudnn_b200_linear_t handle, void *cuda_stream);
 

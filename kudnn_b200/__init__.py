@@ -10,8 +10,9 @@ from .capi import (  # noqa: F401
     BF16, F16, F32,
     KERNEL_AUTO, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_SIMT, KERNEL_TC, KERNEL_NAMES,
     RES_ELTWISE_MUL, RES_EXT, RES_IDENTICAL, RES_NONE,
-    KudnnError, Linear, LinearDesc, debug_fail_allocation, library, library_path, make_desc, run_static_scratch, shard_range,
-    peer_buffer_close, peer_buffer_create, peer_buffer_destroy, peer_buffer_open,
+    KudnnError, Linear, LinearDesc, activation, debug_fail_allocation, library, library_path, make_desc, run_static_scratch, shard_range,
+    peer_buffer_close, peer_buffer_create, peer_buffer_destroy, peer_buffer_open, rmsnorm,
+    NORM_USE_GLOBAL_STATS, NORM_USE_SCALE,
 )
 
 __all__ = [
@@ -19,6 +20,7 @@ __all__ = [
     "BF16", "F16", "F32",
     "KERNEL_AUTO", "KERNEL_GEMV_FMA", "KERNEL_GEMV_MMA", "KERNEL_SIMT", "KERNEL_TC", "KERNEL_NAMES",
     "RES_ELTWISE_MUL", "RES_EXT", "RES_IDENTICAL", "RES_NONE",
-    "KudnnError", "Linear", "LinearDesc", "debug_fail_allocation", "library", "library_path", "make_desc", "run_static_scratch", "shard_range",
-    "peer_buffer_close", "peer_buffer_create", "peer_buffer_destroy", "peer_buffer_open",
+    "KudnnError", "Linear", "LinearDesc", "activation", "debug_fail_allocation", "library", "library_path", "make_desc", "run_static_scratch", "shard_range",
+    "peer_buffer_close", "peer_buffer_create", "peer_buffer_destroy", "peer_buffer_open", "rmsnorm",
+    "NORM_USE_GLOBAL_STATS", "NORM_USE_SCALE",
 ]

@@ -27,7 +27,7 @@ NVCC_FLAGS = [
     "-I", os.path.join(_ROOT, "include"),
 ]
 
-CUDA_SOURCES = ["linear_api.cu", "simt_gemm.cu", "gemv.cu", "tc_gemm.cu", "pack.cu", "static_scratch.cu", "peer.cu"]
+CUDA_SOURCES = ["linear_api.cu", "simt_gemm.cu", "gemv.cu", "tc_gemm.cu", "pack.cu", "static_scratch.cu", "peer.cu", "eltwise.cu", "eltwise_api.cu"]
 
 
 def _nvcc():

@@ -63,6 +63,7 @@ EXPORTS = [
     "kudnn_b200_device_count", "kudnn_b200_linear_set_mirrors", "kudnn_b200_peer_buffer_create",
     "kudnn_b200_peer_buffer_open", "kudnn_b200_peer_buffer_close", "kudnn_b200_peer_buffer_destroy",
     "kudnn_b200_linear_unpack", "kudnn_b200_debug_set_wait", "kudnn_b200_debug_fail_allocation",
+    "kudnn_b200_activation_validate", "kudnn_b200_activation_run", "kudnn_b200_rmsnorm_validate", "kudnn_b200_rmsnorm_run",
 ]
 
 _lib = None
@@ -98,6 +99,10 @@ def library():
     lib.kudnn_b200_peer_buffer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
     lib.kudnn_b200_peer_buffer_close.argtypes = [vp]
     lib.kudnn_b200_peer_buffer_destroy.argtypes = [vp]
+    lib.kudnn_b200_activation_validate.argtypes = [i64, i32, i32, i32]
+    lib.kudnn_b200_activation_run.argtypes = [vp, vp, i64, i32, i32, i32, ctypes.c_float, vp]
+    lib.kudnn_b200_rmsnorm_validate.argtypes = [i64, i64, i32, i32]
+    lib.kudnn_b200_rmsnorm_run.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32, i32, ctypes.c_float, vp]
     lib.kudnn_b200_linear_unpack.argtypes = [vp]
     lib.kudnn_b200_debug_set_wait.argtypes = [vp, ctypes.c_longlong, i32]
     lib.kudnn_b200_debug_fail_allocation.argtypes = [i32]
@@ -200,6 +205,20 @@ def peer_buffer_close(ptr):
 
 def peer_buffer_destroy(ptr):
     _check(library().kudnn_b200_peer_buffer_destroy(ptr))
+
+
+NORM_USE_GLOBAL_STATS, NORM_USE_SCALE, NORM_USE_SHIFT, NORM_FUSE_RELU = 1, 2, 4, 8
+
+
+def activation(src, dst, count, src_dtype, dst_dtype, act, alpha=0.0, stream=None):
+    """Stand-alone activation pass; src and dst both device (asynchronous on `stream`) or both host memory."""
+    _check(library().kudnn_b200_activation_run(_ptr(src), _ptr(dst), count, src_dtype, dst_dtype, act, alpha, stream))
+
+
+def rmsnorm(src, dst, rows, axis, dtype, scale=None, variance=None, flags=0, save_stats=False, eps=1e-6, stream=None):
+    """RMS normalisation over the last axis of a dense [rows, axis] tensor; device or host pointers."""
+    _check(library().kudnn_b200_rmsnorm_run(_ptr(src), _ptr(dst), _ptr(scale), _ptr(variance), rows, axis, dtype, flags,
+                                            1 if save_stats else 0, eps, stream))
 
 
 def debug_fail_allocation(nth):

@@ -99,4 +99,11 @@ cudaError_t launch_pack_blocks(const void *src, long long rows, long long k, lon
 cudaError_t launch_split_tf32(const void *src, long long rows, long long k, long long s_row, long long s_k, float *dst,
                               long long ldd, long long k_pad, int is_weight, cudaStream_t stream);
 
+// Stand-alone element-wise activation and RMS normalisation (eltwise.cu); device pointers.
+cudaError_t launch_activation(const void *src, int src_dtype, void *dst, int dst_dtype, long long count, int act, float alpha,
+                              int sm_count, cudaStream_t stream);
+cudaError_t launch_rmsnorm(const void *src, void *dst, const void *scale, float *variance, long long rows, long long axis,
+                           int dtype, int use_stats, int use_scale, int save_stats, float eps, int sm_count,
+                           cudaStream_t stream);
+
 }  // namespace kb

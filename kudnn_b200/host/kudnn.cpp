@@ -1045,4 +1045,217 @@ int LinearActivationResFWD::LastKernel() const noexcept
     return pImpl->LastKernel();
 }
 
+// ------------------------------------------------------------------------------------------------ NormalizationFlags
+
+NormalizationFlags operator&(const NormalizationFlags &lhs, const NormalizationFlags &rhs)
+{
+    return static_cast<NormalizationFlags>(static_cast<std::uint32_t>(lhs) & static_cast<std::uint32_t>(rhs));
+}
+NormalizationFlags operator|(const NormalizationFlags &lhs, const NormalizationFlags &rhs)
+{
+    return static_cast<NormalizationFlags>(static_cast<std::uint32_t>(lhs) | static_cast<std::uint32_t>(rhs));
+}
+NormalizationFlags &operator&=(NormalizationFlags &lhs, const NormalizationFlags &rhs)
+{
+    lhs = lhs & rhs;
+    return lhs;
+}
+NormalizationFlags &operator|=(NormalizationFlags &lhs, const NormalizationFlags &rhs)
+{
+    lhs = lhs | rhs;
+    return lhs;
+}
+
+// ------------------------------------------------------------------------------------------------ ActivationLayerFWD
+
+namespace Detail {
+struct EltwiseState {
+    int64_t count;
+    int srcType, dstType, kind;
+    float alpha;
+    void *stream = nullptr;
+};
+struct RmsNormState {
+    int64_t rows, axis;
+    int type, flags;
+    void *stream = nullptr;
+};
+}  // namespace Detail
+
+// The checks of the reference in its order (src/dnn/src/kudnn_eltwise.cpp:1479-1516); functions and element types the
+// GPU path does not implement are UNSUPPORTED, the answer the reference gives for what it does not implement.
+Status ActivationLayerFWD::ValidateInput(const TensorInfo &srcInfo, const TensorInfo &dstInfo, ActivationFunction kind,
+                                         float alpha, float beta) noexcept(false)
+{
+    if (srcInfo.GetLayout() != dstInfo.GetLayout()) {
+        return Status::BAD_ARGUMENTS;
+    }
+    const auto isFloat = [](Element::TypeT t) {
+        return t == Element::TypeT::F32 || t == Element::TypeT::F16 || t == Element::TypeT::BF16;
+    };
+    if (!isFloat(srcInfo.GetType()) || !isFloat(dstInfo.GetType())) {
+        return Status::UNSUPPORTED;  // the reference also takes S32 / S8 / U8 for RELU and LINEAR
+    }
+    switch (kind) {
+        case ActivationFunction::RELU:
+        case ActivationFunction::TANH:
+        case ActivationFunction::SIGMOID:
+        case ActivationFunction::GELU_TANH:
+        case ActivationFunction::SWISH:
+        case ActivationFunction::GELU_ERF:
+            break;
+        default:
+            return Status::UNSUPPORTED;
+    }
+    (void)alpha;
+    (void)beta;
+    if (!srcInfo.IsDense() || !dstInfo.IsDense()) {
+        return Status::UNSUPPORTED;
+    }
+    if (srcInfo.GetTotalTensorSize() == 0 || srcInfo.GetDims() != dstInfo.GetDims()) {
+        return Status::UNSUPPORTED;
+    }
+    return Status::SUCCESS;
+}
+
+ActivationLayerFWD::ActivationLayerFWD(const TensorInfo &srcInfo, const TensorInfo &dstInfo, ActivationFunction kind,
+                                       float alpha, float beta) noexcept(false)
+{
+    Service::ThrowOnStatus(ValidateInput(srcInfo, dstInfo, kind, alpha, beta), "Activation Layer");
+    pImpl = std::make_unique<Detail::EltwiseState>();
+    pImpl->count = static_cast<int64_t>(srcInfo.GetTotalTensorSize());
+    pImpl->srcType = DtypeCode(srcInfo.GetType());
+    pImpl->dstType = DtypeCode(dstInfo.GetType());
+    pImpl->kind = ActivationCode(kind);
+    pImpl->alpha = alpha;
+}
+ActivationLayerFWD::ActivationLayerFWD(const ActivationLayerFWD &other) noexcept(false)
+    : pImpl(std::make_unique<Detail::EltwiseState>(*other.pImpl))
+{
+}
+ActivationLayerFWD::ActivationLayerFWD(ActivationLayerFWD &&other) noexcept = default;
+ActivationLayerFWD &ActivationLayerFWD::operator=(const ActivationLayerFWD &other) noexcept(false)
+{
+    if (this != &other) {
+        pImpl = std::make_unique<Detail::EltwiseState>(*other.pImpl);
+    }
+    return *this;
+}
+ActivationLayerFWD &ActivationLayerFWD::operator=(ActivationLayerFWD &&other) noexcept = default;
+ActivationLayerFWD::~ActivationLayerFWD() noexcept = default;
+
+void ActivationLayerFWD::Run(const void *src, void *dst) const noexcept(false)
+{
+    if (src == nullptr || dst == nullptr) {
+        throw Service::LogicError{"Activation Layer: one of input matrices is nullptr"};
+    }
+    const int rc = kudnn_b200_activation_run(src, dst, pImpl->count, pImpl->srcType, pImpl->dstType, pImpl->kind,
+                                             pImpl->alpha, pImpl->stream);
+    if (rc != KUDNN_B200_OK) {
+        ThrowCabi(rc, "Activation Layer");
+    }
+}
+void ActivationLayerFWD::SetStream(void *cudaStream) noexcept
+{
+    pImpl->stream = cudaStream;
+}
+
+// ------------------------------------------------------------------------------------------------ RMSNormalizationLayerFWD
+
+// src/dnn/src/kudnn_rms_normalization_fwd.cpp:333-369, check for check; bf16 and fp32 pass the type checks as well.
+Status RMSNormalizationLayerFWD::ValidateInput(const TensorInfo &srcInfo, const TensorInfo &statsInfo,
+                                               const TensorInfo &scaleInfo, const TensorInfo &dstInfo,
+                                               NormalizationFlags flags) noexcept(false)
+{
+    if (static_cast<bool>(flags & NormalizationFlags::FUSE_NORM_RELU)) {
+        return Status::UNSUPPORTED;
+    }
+    if (srcInfo.GetDims() != dstInfo.GetDims()) {
+        return Status::BAD_ARGUMENTS;
+    }
+    const Element::TypeT t = srcInfo.GetType();
+    if ((t != Element::TypeT::F16 && t != Element::TypeT::BF16 && t != Element::TypeT::F32) || dstInfo.GetType() != t) {
+        return Status::UNSUPPORTED;
+    }
+    if (static_cast<bool>(flags & NormalizationFlags::USE_SCALE) && scaleInfo.GetType() != t) {
+        return Status::UNSUPPORTED;
+    }
+    if ((srcInfo.GetNumDims() - 1) != statsInfo.GetNumDims()) {
+        return Status::BAD_ARGUMENTS;
+    }
+    if (srcInfo.GetTotalTensorSize() == 0) {
+        return Status::UNSUPPORTED;
+    }
+    if (scaleInfo.GetNumDims() != 1) {
+        return Status::BAD_ARGUMENTS;
+    }
+    if (srcInfo.GetDims()[srcInfo.GetNumDims() - 1] != scaleInfo.GetDims()[0]) {
+        return Status::BAD_ARGUMENTS;
+    }
+    for (SizeType i = 0; i < statsInfo.GetNumDims(); ++i) {
+        if (srcInfo.GetDims()[i] != statsInfo.GetDims()[i]) {
+            return Status::BAD_ARGUMENTS;
+        }
+    }
+    if (!srcInfo.IsDense() || !statsInfo.IsDense() || !scaleInfo.IsDense() || !dstInfo.IsDense()) {
+        return Status::UNSUPPORTED;
+    }
+    // the GPU kernel normalises rows that are contiguous in memory: plain row-major tensors
+    if (srcInfo.GetLayout() != srcInfo.GetStandardABXLayout() || dstInfo.GetLayout() != srcInfo.GetLayout() ||
+        statsInfo.GetLayout() != statsInfo.GetStandardABXLayout()) {
+        return Status::UNSUPPORTED;
+    }
+    return Status::SUCCESS;
+}
+
+RMSNormalizationLayerFWD::RMSNormalizationLayerFWD(const TensorInfo &srcInfo, const TensorInfo &statsInfo,
+                                                   const TensorInfo &scaleInfo, const TensorInfo &dstInfo,
+                                                   NormalizationFlags flags) noexcept(false)
+{
+    Service::ThrowOnStatus(ValidateInput(srcInfo, statsInfo, scaleInfo, dstInfo, flags), "Normalization Layer");
+    pImpl = std::make_unique<Detail::RmsNormState>();
+    pImpl->axis = static_cast<int64_t>(srcInfo.GetDims()[srcInfo.GetNumDims() - 1]);
+    pImpl->rows = static_cast<int64_t>(srcInfo.GetTotalTensorSize()) / pImpl->axis;
+    pImpl->type = DtypeCode(srcInfo.GetType());
+    pImpl->flags = static_cast<int>(static_cast<std::uint32_t>(flags));
+}
+RMSNormalizationLayerFWD::RMSNormalizationLayerFWD(const RMSNormalizationLayerFWD &other) noexcept(false)
+    : pImpl(std::make_unique<Detail::RmsNormState>(*other.pImpl))
+{
+}
+RMSNormalizationLayerFWD::RMSNormalizationLayerFWD(RMSNormalizationLayerFWD &&other) noexcept = default;
+RMSNormalizationLayerFWD &RMSNormalizationLayerFWD::operator=(const RMSNormalizationLayerFWD &other) noexcept(false)
+{
+    if (this != &other) {
+        pImpl = std::make_unique<Detail::RmsNormState>(*other.pImpl);
+    }
+    return *this;
+}
+RMSNormalizationLayerFWD &RMSNormalizationLayerFWD::operator=(RMSNormalizationLayerFWD &&other) noexcept = default;
+RMSNormalizationLayerFWD::~RMSNormalizationLayerFWD() noexcept = default;
+
+void RMSNormalizationLayerFWD::Run(const void *src, void *dst, const void *scale, float *variance, bool saveStats,
+                                   const float eps) const noexcept(false)
+{
+    // src/dnn/src/kudnn_rms_normalization_fwd.cpp:213-226
+    if (src == nullptr || dst == nullptr) {
+        throw Service::LogicError{"Normalization: one of input matrices is nullptr"};
+    }
+    if (((pImpl->flags & KUDNN_B200_NORM_USE_GLOBAL_STATS) != 0 || saveStats) && variance == nullptr) {
+        throw Service::LogicError{"Normalization: one of input matrices is nullptr"};
+    }
+    if ((pImpl->flags & KUDNN_B200_NORM_USE_SCALE) != 0 && scale == nullptr) {
+        throw Service::LogicError{"Normalization Layer: one of input matrices is nullptr"};
+    }
+    const int rc = kudnn_b200_rmsnorm_run(src, dst, scale, variance, pImpl->rows, pImpl->axis, pImpl->type, pImpl->flags,
+                                          saveStats ? 1 : 0, eps, pImpl->stream);
+    if (rc != KUDNN_B200_OK) {
+        ThrowCabi(rc, "Normalization Layer");
+    }
+}
+void RMSNormalizationLayerFWD::SetStream(void *cudaStream) noexcept
+{
+    pImpl->stream = cudaStream;
+}
+
 }  // namespace KuDNN

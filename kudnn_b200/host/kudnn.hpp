@@ -400,9 +400,71 @@ enum class ResOpsFunction {
     RES_ELTWISE_MUL   // extension: linearRes = (a.b + bias) * res, element by element
 };
 
+// flags of the normalisation layers (src/dnn/include/types/kudnn_normalization.hpp:18-29)
+enum class NormalizationFlags : std::uint32_t {
+    NONE = 0x0U,
+    USE_GLOBAL_STATS = 0x1U,
+    USE_SCALE = 0x2U,
+    USE_SHIFT = 0x4U,
+    FUSE_NORM_RELU = 0x8U
+};
+KUDNN_API_PUBLIC NormalizationFlags operator&(const NormalizationFlags &lhs, const NormalizationFlags &rhs);
+KUDNN_API_PUBLIC NormalizationFlags operator|(const NormalizationFlags &lhs, const NormalizationFlags &rhs);
+KUDNN_API_PUBLIC NormalizationFlags &operator&=(NormalizationFlags &lhs, const NormalizationFlags &rhs);
+KUDNN_API_PUBLIC NormalizationFlags &operator|=(NormalizationFlags &lhs, const NormalizationFlags &rhs);
+
 namespace Detail {
 class LinearCore;
+struct EltwiseState;
+struct RmsNormState;
 }
+
+// Stand-alone activation pass (src/dnn/include/operations/kudnn_eltwise.hpp:62-76).  Forward functions implemented on
+// the GPU: RELU, TANH, SIGMOID, GELU_TANH, SWISH, GELU_ERF; the others validate as UNSUPPORTED.  src and dst may be
+// host memory, as in the reference, or device memory.
+class KUDNN_API_PUBLIC ActivationLayerFWD final {
+public:
+    using SizeType = ::KuDNN::SizeType;
+    static Status ValidateInput(const TensorInfo &srcInfo, const TensorInfo &dstInfo, ActivationFunction kind,
+                                float alpha = 0.0f, float beta = 0.0f) noexcept(false);
+    ActivationLayerFWD(const TensorInfo &srcInfo, const TensorInfo &dstInfo, ActivationFunction kind, float alpha = 0.0f,
+                       float beta = 0.0f) noexcept(false);
+    ActivationLayerFWD(const ActivationLayerFWD &other) noexcept(false);
+    ActivationLayerFWD(ActivationLayerFWD &&other) noexcept;
+    ActivationLayerFWD &operator=(const ActivationLayerFWD &other) noexcept(false);
+    ActivationLayerFWD &operator=(ActivationLayerFWD &&other) noexcept;
+    void Run(const void *src, void *dst) const noexcept(false);
+    ~ActivationLayerFWD() noexcept;
+
+    void SetStream(void *cudaStream) noexcept;  // extension: stream for device-pointer runs
+
+private:
+    std::unique_ptr<Detail::EltwiseState> pImpl;
+};
+
+// RMS normalisation over the last dimension (src/dnn/include/operations/kudnn_rms_normalization.hpp:26-44).  The
+// reference accepts fp16 tensors only; bf16 and fp32 are accepted here as well.  The last logical dimension must be
+// the innermost one in memory.
+class KUDNN_API_PUBLIC RMSNormalizationLayerFWD final {
+public:
+    using SizeType = ::KuDNN::SizeType;
+    static Status ValidateInput(const TensorInfo &srcInfo, const TensorInfo &statsInfo, const TensorInfo &scaleInfo,
+                                const TensorInfo &dstInfo, NormalizationFlags flags) noexcept(false);
+    RMSNormalizationLayerFWD(const TensorInfo &srcInfo, const TensorInfo &statsInfo, const TensorInfo &scaleInfo,
+                             const TensorInfo &dstInfo, NormalizationFlags flags) noexcept(false);
+    RMSNormalizationLayerFWD(const RMSNormalizationLayerFWD &other) noexcept(false);
+    RMSNormalizationLayerFWD(RMSNormalizationLayerFWD &&other) noexcept;
+    RMSNormalizationLayerFWD &operator=(const RMSNormalizationLayerFWD &other) noexcept(false);
+    RMSNormalizationLayerFWD &operator=(RMSNormalizationLayerFWD &&other) noexcept;
+    void Run(const void *src, void *dst, const void *scale, float *variance, bool saveStats, const float eps) const
+        noexcept(false);
+    ~RMSNormalizationLayerFWD() noexcept;
+
+    void SetStream(void *cudaStream) noexcept;
+
+private:
+    std::unique_ptr<Detail::RmsNormState> pImpl;
+};
 
 class KUDNN_API_PUBLIC Gemm final {
 public:

@@ -682,6 +682,130 @@ void FailurePathCases()
     Report("Gemm.Run_after_allocation_failure_values", worst <= 1e-4, "worst " + std::to_string(worst));
 }
 
+// ---- the operators either side of Linear: contract cases of eltwise_gtest.cpp:172-190 and rmsnorm_gtest.cpp:169-300
+
+void EltwiseAndNormContractTests()
+{
+    const TensorInfo f32a({2, 3, 4, 5}, Element::TypeT::F32, Layout::ABCD), f32b({2, 3, 4, 5}, Element::TypeT::F32, Layout::ABDC);
+    Report("Eltwise.Validate_ok", ActivationLayerFWD::ValidateInput(f32a, f32a, ActivationFunction::RELU) == Status::SUCCESS);
+    Report("Eltwise.Validate_layout_mismatch",
+           ActivationLayerFWD::ValidateInput(f32a, f32b, ActivationFunction::RELU) == Status::BAD_ARGUMENTS);
+    Report("Eltwise.Validate_unimplemented_kind",
+           ActivationLayerFWD::ValidateInput(f32a, f32a, ActivationFunction::UNIMPLEMENTED) == Status::UNSUPPORTED);
+    const TensorInfo s32({2, 3}, Element::TypeT::S32, Layout::AB);
+    Report("Eltwise.Validate_integer_type", ActivationLayerFWD::ValidateInput(s32, s32, ActivationFunction::TANH) == Status::UNSUPPORTED);
+    ExpectThrow<Service::Unsupported>("Eltwise.Ctor_unsupported_kind",
+                                      [&]() { ActivationLayerFWD op(f32a, f32a, ActivationFunction::UNIMPLEMENTED); });
+    ExpectNoThrow("Eltwise.FWDCopyMoveConstructors", [&]() {
+        ActivationLayerFWD a(f32a, f32a, ActivationFunction::SWISH, 1.0f), b(a), c(std::move(a));
+        ActivationLayerFWD d(f32a, f32a, ActivationFunction::RELU);
+        d = b;
+        d = std::move(c);
+    });
+    ExpectThrow<Service::LogicError>("Eltwise.Run_nullptr", [&]() {
+        ActivationLayerFWD op(f32a, f32a, ActivationFunction::RELU);
+        op.Run(nullptr, nullptr);
+    });
+
+    const TensorInfo src({1, 1, 1}, Element::TypeT::F16, Layout::ABC), stat({1, 1}, Element::TypeT::F32, Layout::AB);
+    const TensorInfo scale({1}, Element::TypeT::F16, Layout::A), scaleS32({1}, Element::TypeT::S32, Layout::A);
+    const TensorInfo srcS32({1, 1, 1}, Element::TypeT::S32, Layout::ABC);
+    ExpectThrow<Service::Unsupported>("RMSnorm.FWDSrcDstType", [&]() {
+        RMSNormalizationLayerFWD op(srcS32, stat, scale, srcS32, NormalizationFlags::NONE);
+    });
+    ExpectThrow<Service::Unsupported>("RMSnorm.FWDScaleType", [&]() {
+        RMSNormalizationLayerFWD op(src, stat, scaleS32, src, NormalizationFlags::USE_SCALE);
+    });
+    ExpectNoThrow("RMSnorm.FWDShiftType", [&]() { RMSNormalizationLayerFWD op(src, stat, scaleS32, src, NormalizationFlags::USE_SHIFT); });
+    ExpectNoThrow("RMSnorm.FWDGlobalStatsType",
+                  [&]() { RMSNormalizationLayerFWD op(src, stat, scaleS32, src, NormalizationFlags::USE_GLOBAL_STATS); });
+    ExpectThrow<Service::Unsupported>("RMSnorm.ForwardFlagType", [&]() {
+        RMSNormalizationLayerFWD op(src, stat, scaleS32, src, NormalizationFlags::FUSE_NORM_RELU);
+    });
+    ExpectNoThrow("RMSnorm.CopyMoveConstructors", [&]() {
+        RMSNormalizationLayerFWD a(src, stat, scale, src, NormalizationFlags::NONE), b(a), c(std::move(a));
+        RMSNormalizationLayerFWD d(src, stat, scale, src, NormalizationFlags::NONE);
+        d = b;
+        d = std::move(c);
+    });
+    const TensorInfo src2({4, 6, 8}, Element::TypeT::F16, Layout::ABC), statBad({4, 5}, Element::TypeT::F32, Layout::AB);
+    const TensorInfo scale8({8}, Element::TypeT::F16, Layout::A), scale7({7}, Element::TypeT::F16, Layout::A);
+    const TensorInfo stat46({4, 6}, Element::TypeT::F32, Layout::AB);
+    Report("RMSnorm.Validate_stats_dims",
+           RMSNormalizationLayerFWD::ValidateInput(src2, statBad, scale8, src2, NormalizationFlags::NONE) == Status::BAD_ARGUMENTS);
+    Report("RMSnorm.Validate_scale_dims",
+           RMSNormalizationLayerFWD::ValidateInput(src2, stat46, scale7, src2, NormalizationFlags::NONE) == Status::BAD_ARGUMENTS);
+    Report("RMSnorm.Validate_ok",
+           RMSNormalizationLayerFWD::ValidateInput(src2, stat46, scale8, src2, NormalizationFlags::USE_SCALE) == Status::SUCCESS);
+    ExpectThrow<Service::LogicError>("RMSnorm.Run_nullptr", [&]() {
+        RMSNormalizationLayerFWD op(src2, stat46, scale8, src2, NormalizationFlags::USE_SCALE);
+        std::vector<uint16_t> x(4 * 6 * 8), y(4 * 6 * 8);
+        op.Run(x.data(), y.data(), nullptr, nullptr, false, 1e-5f);
+    });
+}
+
+// numeric cases on the GPU (host pointers, as the reference tests pass them): ForwardFunc4DF32 of eltwise_gtest.cpp and
+// ForwardFunc{2,3}DF16 of rmsnorm_gtest.cpp against plain loops
+void EltwiseAndNormNumericCases()
+{
+    {
+        const size_t count = 3 * 5 * 7 * 11;
+        TensorInfo info({3, 5, 7, 11}, Element::TypeT::F32, Layout::ABCD);
+        std::mt19937 rng(201);
+        HostTensor x = MakeTensor(count, Element::TypeT::F32, &rng), y = MakeTensor(count, Element::TypeT::F32, nullptr);
+        const ActivationFunction kinds[4] = {ActivationFunction::RELU, ActivationFunction::SWISH, ActivationFunction::GELU_TANH,
+                                             ActivationFunction::GELU_ERF};
+        for (ActivationFunction kind : kinds) {
+            try {
+                ActivationLayerFWD op(info, info, kind, kind == ActivationFunction::SWISH ? 1.0f : 0.0f);
+                op.Run(x.data(), y.data());
+                ReadBack(&y);
+                double worst = 0.0;
+                for (size_t i = 0; i < count; ++i) {
+                    worst = std::max(worst, std::fabs(y.values[i] - ActRef(x.values[i], kind, kind == ActivationFunction::SWISH ? 1.0 : 0.0)));
+                }
+                Report("Eltwise.ForwardFunc4DF32_kind" + std::to_string(static_cast<int>(kind)), worst <= 1e-5,
+                       "worst " + std::to_string(worst));
+            } catch (const std::exception &e) {
+                Report("Eltwise.ForwardFunc4DF32", false, e.what());
+            }
+        }
+    }
+    for (int rank = 2; rank <= 3; ++rank) {
+        try {
+            const size_t outer = rank == 2 ? 37 : 5 * 9, axis = 200;
+            TensorInfo src = rank == 2 ? TensorInfo({37, axis}, Element::TypeT::F16, Layout::AB)
+                                       : TensorInfo({5, 9, axis}, Element::TypeT::F16, Layout::ABC);
+            TensorInfo stat = rank == 2 ? TensorInfo({37}, Element::TypeT::F32, Layout::A) : TensorInfo({5, 9}, Element::TypeT::F32, Layout::AB);
+            TensorInfo scale({axis}, Element::TypeT::F16, Layout::A);
+            std::mt19937 rng(210 + rank);
+            HostTensor x = MakeTensor(outer * axis, Element::TypeT::F16, &rng), g = MakeTensor(axis, Element::TypeT::F16, &rng);
+            HostTensor y = MakeTensor(outer * axis, Element::TypeT::F16, nullptr);
+            std::vector<float> var(outer, 0.0f);
+            RMSNormalizationLayerFWD op(src, stat, scale, src, NormalizationFlags::USE_SCALE);
+            op.Run(x.data(), y.data(), g.data(), var.data(), true, 1e-5f);
+            ReadBack(&y);
+            double worst = 0.0, worstVar = 0.0;
+            for (size_t n = 0; n < outer; ++n) {
+                double ss = 0.0;
+                for (size_t i = 0; i < axis; ++i) {
+                    ss += static_cast<double>(x.values[n * axis + i]) * x.values[n * axis + i];
+                }
+                const double v = ss / axis, inv = 1.0 / std::sqrt(v + 1e-5);
+                worstVar = std::max(worstVar, std::fabs(var[n] - v));
+                for (size_t i = 0; i < axis; ++i) {
+                    const double want = x.values[n * axis + i] * g.values[i] * inv;
+                    worst = std::max(worst, std::fabs(y.values[n * axis + i] - want) / (std::fabs(want) + 1.0));
+                }
+            }
+            Report("RMSnorm.ForwardFunc" + std::to_string(rank) + "DF16", worst <= 2e-3 && worstVar <= 1e-5,
+                   "worst " + std::to_string(worst) + " var " + std::to_string(worstVar));
+        } catch (const std::exception &e) {
+            Report("RMSnorm.ForwardFunc" + std::to_string(rank) + "DF16", false, e.what());
+        }
+    }
+}
+
 void NumericTests()
 {
     const Element::TypeT types[3] = {Element::TypeT::F32, Element::TypeT::F16, Element::TypeT::BF16};
@@ -716,6 +840,7 @@ void NumericTests()
     }
     ExtensionCases();
     FailurePathCases();
+    EltwiseAndNormNumericCases();
 }
 
 }  // namespace
@@ -731,6 +856,7 @@ int main(int argc, char **argv)
     ValueTypeTests();
     LinearActivationContractTests();
     LinearResAndGemmContractTests();
+    EltwiseAndNormContractTests();
     if (gpu) {
         if (kudnn_b200_device_count() <= 0) {
             std::printf("FAILED no CUDA device (run with --no-gpu for the host-only cases)\n");

@@ -64,6 +64,12 @@ def load(path=None):
     lib.ko_num_threads.restype = ctypes.c_int
     lib.ko_activation.restype = ctypes.c_float
     lib.ko_activation.argtypes = [ctypes.c_float, ctypes.c_int, ctypes.c_float]
+    lib.ko_activation_run.restype = ctypes.c_int
+    lib.ko_activation_run.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_int, ctypes.c_float]
+    lib.ko_rmsnorm.restype = ctypes.c_int
+    lib.ko_rmsnorm.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
+                                                       ctypes.c_int, ctypes.c_float]
     for name in ("ko_convert_f32_to_bf16", "ko_convert_f32_to_f16", "ko_convert_bf16_to_f32", "ko_convert_f16_to_f32"):
         fn = getattr(lib, name)
         fn.restype = None
@@ -111,3 +117,19 @@ def linear(desc, a, b, c=None, bias=None, res=None, out=None, alpha=1.0, beta=0.
                        alpha, beta, gamma, acc, num_threads)
     if rc != 0:
         raise RuntimeError("ko_linear failed with code %d" % rc)
+
+
+def activation(src, dst, src_dtype, dst_dtype, act, alpha=0.0, lib=None):
+    """Stand-alone activation pass on the CPU; dst is written in place."""
+    lib = lib or load()
+    rc = lib.ko_activation_run(_ptr(src), _ptr(dst), src.size, src_dtype, dst_dtype, act, alpha)
+    if rc != 0:
+        raise RuntimeError("ko_activation_run failed with code %d" % rc)
+
+
+def rmsnorm(src, dst, scale, variance, rows, axis, dtype, flags, save_stats, eps, lib=None):
+    """RMS normalisation over the last axis on the CPU; dst (and variance when save_stats) are written in place."""
+    lib = lib or load()
+    rc = lib.ko_rmsnorm(_ptr(src), _ptr(dst), _ptr(scale), _ptr(variance), rows, axis, dtype, flags, 1 if save_stats else 0, eps)
+    if rc != 0:
+        raise RuntimeError("ko_rmsnorm failed with code %d" % rc)

@@ -30,6 +30,8 @@
  *   gelu_erf               src/dnn/src/kernels/vml/gelu_erf/vml_sve_la_gelu_erf.h:20-28
  *   bf16 out = truncation  src/dnn/src/kernels/vml/vml_sve_base.h:111-118 ; fp16 out = RNE
  *   residual add / ext     src/dnn/src/kudnn_linear_res.cpp:57-122
+ *   stand-alone activation src/dnn/src/kudnn_eltwise.cpp:500-586
+ *   RMS normalisation      src/dnn/src/kernels/rmsnorm/kudnn_rmsnorm_fwd_last_def.hpp:128-180
  * The element-wise product with a gate tensor (KO_RES_ELTWISE_MUL) has no
  * counterpart in the reference (its RES_MUL is a second matrix product,
  * kudnn_linear_res.cpp:188-190); it is defined as rne(f32(c) * f32(gate)).
@@ -539,6 +541,75 @@ int ko_linear(const ko_desc *d, const void *a, const void *b, void *c, const voi
     }
     free(pa);
     free(pb);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ the operators either side of Linear */
+
+/*
+ * Stand-alone activation pass over a dense tensor (ActivationLayerImplFWD::RunSequential,
+ * src/dnn/src/kudnn_eltwise.cpp:500-586): equal types run the typed kernel (fp32 arithmetic, fp16 RNE, bf16
+ * truncation, bf16 relu overflow rule); different types convert to fp32, run the fp32 kernel and convert back with
+ * one rounding to nearest even (:512-523, :577-584).
+ */
+int ko_activation_run(const void *src, void *dst, int64_t count, int src_dtype, int dst_dtype, int act, float alpha)
+{
+    if (src == NULL || dst == NULL || count <= 0) {
+        return -1;
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < count; ++i) {
+        const float y = ko_activation(ko_load(src, src_dtype, i), act, alpha);
+        if (src_dtype == dst_dtype) {
+            ko_store_exact(dst, dst_dtype, i, ko_round_act(y, dst_dtype, act));
+        } else {
+            ko_store_exact(dst, dst_dtype, i, ko_round_rne(y, dst_dtype));
+        }
+    }
+    return 0;
+}
+
+/*
+ * RMS normalisation over the last axis of a dense [rows, axis] tensor (RMSNorm::EvaluateLastAxis,
+ * src/dnn/src/kernels/rmsnorm/kudnn_rmsnorm_fwd_last_def.hpp:128-180): the variance is the mean of the squares,
+ * accumulated in fp32 vector lanes (here 16) and divided by the axis length, or the caller's value with
+ * USE_GLOBAL_STATS (flag 1); the multiplier of an element is scale * (1 / sqrt(variance + eps)) (flag 2, :49-72) or
+ * the inverse root alone; x times the multiplier is computed in fp32 and rounded once.
+ */
+int ko_rmsnorm(const void *src, void *dst, const void *scale, float *variance, int64_t rows, int64_t axis, int dtype,
+               int flags, int save_stats, float eps)
+{
+    const int use_stats = (flags & 1) != 0, use_scale = (flags & 2) != 0;
+    if (src == NULL || dst == NULL || rows <= 0 || axis <= 0 || ((use_stats || save_stats) && variance == NULL) ||
+        (use_scale && scale == NULL)) {
+        return -1;
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < rows; ++n) {
+        float var;
+        if (use_stats) {
+            var = variance[n];
+        } else {
+            float lanes[KO_LANES] = {0};
+            for (int64_t i = 0; i < axis; ++i) {
+                const float x = ko_load(src, dtype, n * axis + i);
+                lanes[i % KO_LANES] += x * x;
+            }
+            float sum = 0.0f;
+            for (int l = 0; l < KO_LANES; ++l) {
+                sum += lanes[l];
+            }
+            var = sum / (float)axis;
+            if (save_stats) {
+                variance[n] = var;
+            }
+        }
+        const float inv = 1.0f / sqrtf(var + eps);
+        for (int64_t i = 0; i < axis; ++i) {
+            const float c = use_scale ? ko_load(scale, dtype, i) * inv : inv;
+            ko_store_exact(dst, dtype, n * axis + i, ko_round_rne(ko_load(src, dtype, n * axis + i) * c, dtype));
+        }
+    }
     return 0;
 }
 

@@ -143,6 +143,19 @@ KUDNN_B200_API int kudnn_b200_linear_run_host(kudnn_b200_linear_t handle, const 
 KUDNN_B200_API int kudnn_b200_linear_run_any(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args,
                                              void *cuda_stream);
 
+/* Execute with HOST pointers on several GPUs of this machine from one process.  The rows of the layer
+ * (KUDNN_B200_SHARD_ROWS: every device gets the whole weight matrix and a block of the rows of a, c, res, out) or its
+ * columns (KUDNN_B200_SHARD_COLS: every device gets all of a and a slab of the columns of b, bias, c, res, out) are
+ * cut into `nshards` pieces, boundaries at multiples of 128 rows / 8 columns; shard i runs on device
+ * i modulo the device count, on a host thread of its own, through a child primitive that packs its weights on first
+ * use and recognises the weight pointer afterwards.  Nothing crosses between devices: every shard's slab goes straight
+ * back into the caller's host tensors, so no gather step is needed.  Returns when all outputs are complete.  No
+ * counterpart in the reference, a single-socket CPU library. */
+#define KUDNN_B200_SHARD_ROWS 0
+#define KUDNN_B200_SHARD_COLS 1
+KUDNN_B200_API int kudnn_b200_linear_run_sharded(kudnn_b200_linear_t handle, const kudnn_b200_linear_args *args,
+                                                 int nshards, int mode);
+
 /* Decode-shaped Linear (m <= 16, 2-D, K-contiguous a and b) that allocates no device memory, for callers that
  * cannot call cudaMalloc when they need the result: engines that have already handed all of HBM to their own pools,
  * plug-ins whose host forbids allocation inside an operator call, decode loops that cannot risk the device

@@ -12,7 +12,7 @@ from .capi import (  # noqa: F401
     RES_ELTWISE_MUL, RES_EXT, RES_IDENTICAL, RES_NONE,
     KudnnError, Linear, LinearDesc, activation, debug_fail_allocation, library, library_path, make_desc, run_static_scratch, shard_range,
     peer_buffer_close, peer_buffer_create, peer_buffer_destroy, peer_buffer_open, rmsnorm,
-    NORM_USE_GLOBAL_STATS, NORM_USE_SCALE,
+    NORM_USE_GLOBAL_STATS, NORM_USE_SCALE, SHARD_COLS, SHARD_ROWS,
 )
 
 __all__ = [
@@ -22,5 +22,5 @@ __all__ = [
     "RES_ELTWISE_MUL", "RES_EXT", "RES_IDENTICAL", "RES_NONE",
     "KudnnError", "Linear", "LinearDesc", "activation", "debug_fail_allocation", "library", "library_path", "make_desc", "run_static_scratch", "shard_range",
     "peer_buffer_close", "peer_buffer_create", "peer_buffer_destroy", "peer_buffer_open", "rmsnorm",
-    "NORM_USE_GLOBAL_STATS", "NORM_USE_SCALE",
+    "NORM_USE_GLOBAL_STATS", "NORM_USE_SCALE", "SHARD_COLS", "SHARD_ROWS",
 ]

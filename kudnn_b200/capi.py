@@ -12,6 +12,8 @@ RES_NONE, RES_EXT, RES_IDENTICAL, RES_ELTWISE_MUL = 0, 1, 2, 3
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_TC = 0, 1, 2, 3, 4
 KERNEL_NAMES = {0: "auto", 1: "simt", 2: "gemv_fma", 3: "gemv_mma", 4: "tc"}
 
+SHARD_ROWS, SHARD_COLS = 0, 1
+
 STATUS_NAMES = {0: "OK", 1: "UNSUPPORTED", 2: "BAD_ARGUMENTS", 3: "ALLOC_FAILED", 4: "CUDA_ERROR", 5: "TIMEOUT",
                 6: "NO_DEVICE"}
 
@@ -63,7 +65,7 @@ EXPORTS = [
     "kudnn_b200_device_count", "kudnn_b200_linear_set_mirrors", "kudnn_b200_peer_buffer_create",
     "kudnn_b200_peer_buffer_open", "kudnn_b200_peer_buffer_close", "kudnn_b200_peer_buffer_destroy",
     "kudnn_b200_linear_unpack", "kudnn_b200_debug_set_wait", "kudnn_b200_debug_fail_allocation",
-    "kudnn_b200_activation_validate", "kudnn_b200_activation_run", "kudnn_b200_rmsnorm_validate", "kudnn_b200_rmsnorm_run",
+    "kudnn_b200_linear_run_sharded", "kudnn_b200_activation_validate", "kudnn_b200_activation_run", "kudnn_b200_rmsnorm_validate", "kudnn_b200_rmsnorm_run",
 ]
 
 _lib = None
@@ -103,6 +105,7 @@ def library():
     lib.kudnn_b200_activation_run.argtypes = [vp, vp, i64, i32, i32, i32, ctypes.c_float, vp]
     lib.kudnn_b200_rmsnorm_validate.argtypes = [i64, i64, i32, i32]
     lib.kudnn_b200_rmsnorm_run.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32, i32, ctypes.c_float, vp]
+    lib.kudnn_b200_linear_run_sharded.argtypes = [vp, ctypes.POINTER(LinearArgs), i32, i32]
     lib.kudnn_b200_linear_unpack.argtypes = [vp]
     lib.kudnn_b200_debug_set_wait.argtypes = [vp, ctypes.c_longlong, i32]
     lib.kudnn_b200_debug_fail_allocation.argtypes = [i32]
@@ -288,6 +291,13 @@ class Linear:
         """Host pointers, as the reference's callers pass them; returns when the outputs are in host memory."""
         args = self._args(a, b, c, bias, res, out, alpha, beta, gamma)
         _check(self._lib.kudnn_b200_linear_run_host(self._h, ctypes.byref(args)))
+
+    def run_sharded(self, a, b, c=None, bias=None, res=None, out=None, alpha=1.0, beta=0.0, gamma=1.0, nshards=1,
+                    mode=SHARD_ROWS):
+        """Host pointers; the rows (SHARD_ROWS) or columns (SHARD_COLS) of the layer are split into `nshards` pieces
+        that run on this machine's GPUs (shard i on device i modulo the device count) from this one process."""
+        args = self._args(a, b, c, bias, res, out, alpha, beta, gamma)
+        _check(self._lib.kudnn_b200_linear_run_sharded(self._h, ctypes.byref(args), nshards, mode))
 
     def check(self, stream=None):
         _check(self._lib.kudnn_b200_linear_check(self._h, stream))

@@ -57,6 +57,8 @@ struct TcOperands {
     long long lda, ldb;   // row pitch in elements
     long long k_total;    // contraction length as laid out (3*k for the split-fp32 form)
     int kind;             // KUDNN_B200_F16 / _BF16 / _F32 (tf32 planes)
+    // batched problems: `batch` matrices per operand, a_bstride / b_bstride elements apart (0: every entry shares one)
+    long long batch = 1, a_bstride = 0, b_bstride = 0;
 };
 struct TcPlan {
     int block_n;   // 128 or 256
@@ -81,14 +83,25 @@ cudaError_t tc_encode_kmajor(void *map128, const void *base, int kind, long long
 cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm_count, bool with_staging, TcPlan *plan);
 // wait_limit_cycles: SM cycles after which a device-side wait gives up (0 = the default of about two seconds);
 // skip_kblock: test hook for the timeout path, -1 = off (see TcParams::skip_kb).
+// bp: batch strides of the epilogue tensors (ignored unless ops.batch > 1)
 cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams &epi, long long m, long long n,
-                      DeviceStatus *status, cudaStream_t stream, long long wait_limit_cycles = 0, int skip_kblock = -1);
+                      DeviceStatus *status, cudaStream_t stream, long long wait_limit_cycles = 0, int skip_kblock = -1,
+                      const BatchParams *bp = nullptr);
+
+// Batched packing: `count` matrices; entry `flat` of the source starts sb[0] * i0 + sb[1] * i1 + sb[2] * i2 elements
+// into the tensor, (i0, i1, i2) the decomposition of flat over the extents (.., n1, n2); entry `flat` of the packed
+// copy starts flat * dst_batch elements into dst.
+struct PackBatch {
+    long long count, n1, n2;
+    long long sb[3];
+    long long dst_batch;
+};
 
 // Packing / conversion kernels.
 // dst[r, kk] (row pitch ldd, K-major) = src[r*s_row + kk*s_k] converted to dst_dtype; columns [k, k_pad) are zeroed.
 cudaError_t launch_pack_kmajor(const void *src, int src_dtype, long long rows, long long k, long long s_row,
                                long long s_k, void *dst, int dst_dtype, long long ldd, long long k_pad,
-                               cudaStream_t stream);
+                               cudaStream_t stream, const PackBatch *batch = nullptr);
 // 16-bit K-major rows (pitch ld elements) -> the decode-packed layout: [ceil(rows / 8)][k_pad / 64] blocks of 1 KiB
 // (8 rows x 64 k, chunk order as described at GemvParams::w_blk), zero padded.
 cudaError_t launch_pack_blocks(const void *src, long long rows, long long k, long long ld, void *dst, long long k_pad,
@@ -97,7 +110,8 @@ cudaError_t launch_pack_blocks(const void *src, long long rows, long long k, lon
 // hi = tf32(x) and lo = tf32(x - hi), activations are laid out [lo | hi | hi] and weights [hi | lo | hi], so that one
 // contraction over the 3 * k_pad columns yields a_lo.b_hi + a_hi.b_lo + a_hi.b_hi.
 cudaError_t launch_split_tf32(const void *src, long long rows, long long k, long long s_row, long long s_k, float *dst,
-                              long long ldd, long long k_pad, int is_weight, cudaStream_t stream);
+                              long long ldd, long long k_pad, int is_weight, cudaStream_t stream,
+                              const PackBatch *batch = nullptr);
 
 // Stand-alone element-wise activation and RMS normalisation (eltwise.cu); device pointers.
 cudaError_t launch_activation(const void *src, int src_dtype, void *dst, int dst_dtype, long long count, int act, float alpha,

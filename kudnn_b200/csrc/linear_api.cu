@@ -10,6 +10,9 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <string>
+#include <thread>
+#include <vector>
 
 namespace {
 
@@ -156,6 +159,18 @@ struct kudnn_b200_linear_s {
     long long plan_m = 0;
     bool plan_staging = false;
     bool plan_valid = false;
+
+    // kudnn_b200_linear_run_sharded: one child primitive per shard, each on its own device with its own copy (or
+    // slab) of the weights
+    struct Shard {
+        kudnn_b200_linear_s *child = nullptr;
+        int device = 0;
+        long long begin = 0, count = 0;
+        const void *weights = nullptr;  // host pointer the child's packed weights were made from
+        DeviceBuffer buf[5];            // column shards: a, bias slice, c slab, res slab, out slab
+    };
+    std::vector<Shard> shards;
+    int shard_mode = -1, shard_count = 0;
 
     // host-pointer path: copy-in, compute and copy-out streams with one event pair per row chunk
     static constexpr int kMaxChunks = 16;
@@ -487,9 +502,14 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
     }
 
     // ---- tensor-core kernel
+    // Batched problems take it too: the batch entry is a third coordinate of the tile scheduler and of the tensor
+    // maps.  An operand is read in place when its matrices are K-major and its batch entries lie a single stride
+    // apart (or are one shared matrix); anything else is packed first, all entries in one launch.
+    const long long nb = pr.batch_count;
     const bool tc_types = d.a_dtype == d.b_dtype;
-    const bool tc_worth = static_cast<double>(d.m) * d.n * d.k >= 1.0e6 * 8 && d.k >= 32;
-    if (two_d && tc_types && (forced == KUDNN_B200_KERNEL_TC || (forced == KUDNN_B200_KERNEL_AUTO && tc_worth))) {
+    const bool tc_worth = static_cast<double>(d.m) * d.n * d.k * static_cast<double>(nb) >= 1.0e6 * 8 && d.k >= 32;
+    const bool tc_batch_ok = nb == 1 || (nb <= 65535 && pr.epi.n_mirrors == 0);
+    if (tc_batch_ok && tc_types && (forced == KUDNN_B200_KERNEL_TC || (forced == KUDNN_B200_KERNEL_AUTO && tc_worth))) {
         if (!kb::tc_available()) {
             if (forced == KUDNN_B200_KERNEL_TC) {
                 return fail(KUDNN_B200_UNSUPPORTED, "tensor-core kernel unavailable: %s", kb::tc_unavailable_reason());
@@ -497,17 +517,75 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
         } else {
             kb::TcOperands ops;
             ops.kind = d.a_dtype;
+            ops.batch = nb;
             const bool f32 = d.a_dtype == KUDNN_B200_F32;
+            const int es = kb::dtype_size(d.a_dtype);
+            const long long e3[3] = {batch_extent(d, 0), batch_extent(d, 1), batch_extent(d, 2)};
+            // single stride between consecutive flat batch entries, 0 when all entries share the matrix; false when
+            // the three batch strides do not reduce to one
+            auto flat_stride = [&](const int64_t sb[3], long long *stride) {
+                long long unit = -1;
+                long long inner = 1;
+                bool any = false, all_zero = true;
+                for (int i = 2; i >= 0; --i) {
+                    if (e3[i] > 1) {
+                        any = true;
+                        if (sb[i] != 0) {
+                            all_zero = false;
+                        }
+                    }
+                }
+                if (!any || all_zero) {
+                    *stride = 0;
+                    return true;
+                }
+                for (int i = 2; i >= 0; --i) {
+                    if (e3[i] > 1) {
+                        if (sb[i] == 0 || sb[i] % inner != 0) {
+                            return false;
+                        }
+                        const long long u = sb[i] / inner;
+                        if (unit >= 0 && u != unit) {
+                            return false;
+                        }
+                        unit = u;
+                        inner *= e3[i];
+                    }
+                }
+                *stride = unit;
+                return (unit * es) % 16 == 0;
+            };
+            auto pack_batch = [&](const int64_t sb[3], bool shared, long long dst_batch) {
+                kb::PackBatch pb;
+                pb.count = shared ? 1 : nb;
+                pb.n1 = e3[1];
+                pb.n2 = e3[2];
+                for (int i = 0; i < 3; ++i) {
+                    pb.sb[i] = (e3[i] > 1) ? sb[i] : 0;
+                }
+                pb.dst_batch = dst_batch;
+                return pb;
+            };
+            auto all_shared = [&](const int64_t sb[3]) {
+                for (int i = 0; i < 3; ++i) {
+                    if (e3[i] > 1 && sb[i] != 0) {
+                        return false;
+                    }
+                }
+                return true;
+            };
             // weights
+            long long bstride = 0;
             if (use_packed) {
                 ops.b = h->packed_ptr;
                 ops.ldb = h->packed_ld;
                 ops.k_total = h->packed_ktotal;
-            } else if (!f32 && kmajor_ready(args.b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
+            } else if (!f32 && kmajor_ready(args.b, d.b_dtype, d.b_sn, d.b_sk, d.n) && flat_stride(d.b_sb, &bstride)) {
                 ops.b = args.b;
                 ops.ldb = d.b_sn;
                 ops.k_total = d.k;
-            } else {
+                ops.b_bstride = bstride;
+            } else if (nb == 1) {
                 long long ld = 0, kt = 0;
                 const void *raw = nullptr;
                 rc = pack_weights(h, args.b, &h->b_scratch, false, stream, &ld, &kt, &raw, &launches);
@@ -517,44 +595,59 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
                 ops.b = h->b_scratch.ptr;
                 ops.ldb = ld;
                 ops.k_total = kt;
-            }
-            // activations
-            if (f32) {
-                const long long k_pad = round_up(d.k, 32);
-                const long long pitch = 3 * k_pad;
-                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * pitch * sizeof(float));
+            } else {
+                const bool shared = all_shared(d.b_sb);
+                const long long k_pad = round_up(d.k, f32 ? 32 : 8);
+                const long long pitch = f32 ? 3 * k_pad : k_pad;
+                const long long per = d.n * pitch;
+                cudaError_t e = h->b_scratch.reserve(static_cast<size_t>(shared ? 1 : nb) * per * es);
                 if (e != cudaSuccess) {
-                    return fail_cuda(e, "activation planes");
+                    return fail_cuda(e, "packed weights");
                 }
-                e = kb::launch_split_tf32(args.a, d.m, d.k, d.a_sm, d.a_sk, static_cast<float *>(h->a_scratch.ptr), pitch,
-                                          k_pad, 0, stream);
+                const kb::PackBatch pb = pack_batch(d.b_sb, shared, per);
+                e = f32 ? kb::launch_split_tf32(args.b, d.n, d.k, d.b_sn, d.b_sk, static_cast<float *>(h->b_scratch.ptr), pitch,
+                                                k_pad, 1, stream, &pb)
+                        : kb::launch_pack_kmajor(args.b, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, h->b_scratch.ptr, d.b_dtype, pitch,
+                                                 k_pad, stream, &pb);
                 if (e != cudaSuccess) {
-                    return fail_cuda(e, "activation split kernel");
+                    return fail_cuda(e, "weight pack kernel");
                 }
                 launches += 1;
-                ops.a = h->a_scratch.ptr;
-                ops.lda = pitch;
-            } else if (kmajor_ready(args.a, d.a_dtype, d.a_sm, d.a_sk, d.m)) {
+                ops.b = h->b_scratch.ptr;
+                ops.ldb = pitch;
+                ops.k_total = f32 ? 3 * k_pad : d.k;
+                ops.b_bstride = shared ? 0 : per;
+            }
+            // activations
+            long long astride = 0;
+            if (!f32 && kmajor_ready(args.a, d.a_dtype, d.a_sm, d.a_sk, d.m) && flat_stride(d.a_sb, &astride)) {
                 ops.a = args.a;
                 ops.lda = d.a_sm;
+                ops.a_bstride = astride;
             } else {
-                const long long k_pad = round_up(d.k, 8);
-                const long long pitch = k_pad;
-                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * pitch * 2);
+                const bool shared = all_shared(d.a_sb);
+                const long long k_pad = round_up(d.k, f32 ? 32 : 8);
+                const long long pitch = f32 ? 3 * k_pad : k_pad;
+                const long long per = d.m * pitch;
+                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(shared ? 1 : nb) * per * es);
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "packed activations");
                 }
-                e = kb::launch_pack_kmajor(args.a, d.a_dtype, d.m, d.k, d.a_sm, d.a_sk, h->a_scratch.ptr, d.a_dtype, pitch,
-                                           k_pad, stream);
+                const kb::PackBatch pb = pack_batch(d.a_sb, shared, per);
+                e = f32 ? kb::launch_split_tf32(args.a, d.m, d.k, d.a_sm, d.a_sk, static_cast<float *>(h->a_scratch.ptr), pitch,
+                                                k_pad, 0, stream, &pb)
+                        : kb::launch_pack_kmajor(args.a, d.a_dtype, d.m, d.k, d.a_sm, d.a_sk, h->a_scratch.ptr, d.a_dtype, pitch,
+                                                 k_pad, stream, &pb);
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "activation pack kernel");
                 }
                 launches += 1;
                 ops.a = h->a_scratch.ptr;
                 ops.lda = pitch;
+                ops.a_bstride = shared ? 0 : per;
             }
             const bool staging = pr.epi.n_mirrors > 0;
-            if (!(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b && h->plan_m == d.m && h->plan_staging == staging)) {
+            if (nb > 1 || !(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b && h->plan_m == d.m && h->plan_staging == staging)) {
                 cudaError_t e = kb::tc_make_plan(ops, d.m, d.n, h->sm_count, staging, &h->tc_plan);
                 if (e != cudaSuccess) {
                     return fail_cuda(e, "tensor map encoding");
@@ -563,12 +656,12 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
                 h->plan_b = ops.b;
                 h->plan_m = d.m;
                 h->plan_staging = staging;
-                h->plan_valid = true;
+                h->plan_valid = nb == 1;
                 if (const char *dbg = std::getenv("KUDNN_B200_DEBUG")) {
                     if (*dbg != '\0' && *dbg != '0') {
-                        std::fprintf(stderr, "kudnn_b200: tensor-core plan m=%lld n=%lld k=%lld: tile %s x %d, %d stages, grid %d, "
-                                             "k splits %d, narrow tail from tile %d, %zu bytes of shared memory\n",
-                                     static_cast<long long>(d.m), static_cast<long long>(d.n), static_cast<long long>(d.k),
+                        std::fprintf(stderr, "kudnn_b200: tensor-core plan batch=%lld m=%lld n=%lld k=%lld: tile %s x %d, %d stages, "
+                                             "grid %d, k splits %d, narrow tail from tile %d, %zu bytes of shared memory\n",
+                                     nb, static_cast<long long>(d.m), static_cast<long long>(d.n), static_cast<long long>(d.k),
                                      h->tc_plan.pair ? "256 (CTA pair)" : "128", h->tc_plan.block_n, h->tc_plan.stages,
                                      h->tc_plan.grid, h->tc_plan.splits, h->tc_plan.pair ? h->tc_plan.narrow_from : -1, h->tc_plan.smem_bytes);
                     }
@@ -576,7 +669,7 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
             }
             cudaError_t e = kb::launch_tc(ops, h->tc_plan, pr.epi, d.m, d.n,
                                           static_cast<kb::DeviceStatus *>(h->status.ptr), stream, h->wait_limit,
-                                          h->skip_kblock);
+                                          h->skip_kblock, &pr.batch);
             if (e != cudaSuccess) {
                 return fail_cuda(e, "tensor-core kernel launch");
             }
@@ -585,7 +678,7 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
             return KUDNN_B200_OK;
         }
     } else if (forced == KUDNN_B200_KERNEL_TC) {
-        return fail(KUDNN_B200_UNSUPPORTED, "the tensor-core kernel takes 2-D problems with equal input types only");
+        return fail(KUDNN_B200_UNSUPPORTED, "the tensor-core kernel takes problems with equal input types only");
     }
 
     // ---- general kernel
@@ -884,6 +977,22 @@ int kudnn_b200_linear_destroy(kudnn_b200_linear_t h)
     if (h == nullptr) {
         return KUDNN_B200_OK;
     }
+    if (!h->shards.empty()) {
+        int cur = -1;
+        (void)cudaGetDevice(&cur);
+        for (auto &sh : h->shards) {
+            cudaSetDevice(sh.device);
+            for (auto &b : sh.buf) {
+                b.release();
+            }
+            kudnn_b200_linear_destroy(sh.child);
+        }
+        h->shards.clear();
+        if (cur >= 0) {
+            cudaSetDevice(cur);
+        }
+        (void)cudaGetLastError();
+    }
     if (h->device >= 0) {
         int cur = 0;
         if (cudaGetDevice(&cur) == cudaSuccess && cur != h->device) {
@@ -1101,6 +1210,200 @@ int kudnn_b200_linear_run_host(kudnn_b200_linear_t h, const kudnn_b200_linear_ar
         return fail_cuda(e, "run_host");
     }
     return read_status(h);
+}
+
+int kudnn_b200_linear_run_sharded(kudnn_b200_linear_t h, const kudnn_b200_linear_args *args, int nshards, int mode)
+{
+    if (h == nullptr || args == nullptr || nshards < 1 || nshards > 64 ||
+        (mode != KUDNN_B200_SHARD_ROWS && mode != KUDNN_B200_SHARD_COLS)) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run_sharded: bad argument");
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    const kudnn_b200_linear_desc &d = h->d;
+    if (batch_extent(d, 0) * batch_extent(d, 1) * batch_extent(d, 2) != 1) {
+        return fail(KUDNN_B200_UNSUPPORTED, "run_sharded: batched problems are not sharded");
+    }
+    if (args->a == nullptr || args->b == nullptr || (d.has_bias != 0) != (args->bias != nullptr) ||
+        (d.res_op != KUDNN_B200_RES_NONE ? (args->res == nullptr || args->out == nullptr) : args->c == nullptr)) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "run_sharded: pointers do not match the descriptor");
+    }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, args->a) == cudaSuccess &&
+        (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged)) {
+        return fail(KUDNN_B200_UNSUPPORTED, "run_sharded takes host pointers (device-resident shards belong to one process per "
+                                            "GPU, see kudnn_b200_shard_range and kudnn_b200_linear_set_mirrors)");
+    }
+    (void)cudaGetLastError();
+    const int ndev = kudnn_b200_device_count();
+    if (ndev <= 0) {
+        return fail(KUDNN_B200_NO_DEVICE, "run_sharded: no CUDA device");
+    }
+    const bool cols = mode == KUDNN_B200_SHARD_COLS;
+    const bool has_res = d.res_op != KUDNN_B200_RES_NONE;
+    if (cols && (args->beta != 0.0f || d.a_sk != 1 || d.c_sn != 1 || (has_res && (d.res_sn != 1 || d.out_sn != 1)) ||
+                 (d.has_bias != 0 && d.bias_sm != 0))) {
+        return fail(KUDNN_B200_UNSUPPORTED, "run_sharded by columns needs beta = 0, row-major a / c / res / out and a bias that "
+                                            "is one value per column");
+    }
+    // (re)build the children when the split changes
+    if (h->shard_mode != mode || h->shard_count != nshards) {
+        for (auto &sh : h->shards) {
+            cudaSetDevice(sh.device);
+            for (auto &b : sh.buf) {
+                b.release();
+            }
+            kudnn_b200_linear_destroy(sh.child);
+        }
+        h->shards.clear();
+        h->shards.resize(nshards);
+        for (int i = 0; i < nshards; ++i) {
+            Handle::Shard &sh = h->shards[i];
+            int64_t begin = 0, count = 0;
+            kudnn_b200_shard_range(cols ? d.n : d.m, nshards, i, cols ? 8 : 128, &begin, &count);
+            sh.begin = begin;
+            sh.count = count;
+            sh.device = i % ndev;
+            if (count == 0) {
+                continue;
+            }
+            kudnn_b200_linear_desc sub = d;
+            if (cols) {
+                // on the device a shard is a compact problem: its slab of c / res / out has n_local columns
+                sub.n = count;
+                sub.c_sm = sub.res_sm = sub.out_sm = count;
+                sub.a_sm = d.k;
+            } else {
+                sub.m = count;
+            }
+            int rc = kudnn_b200_linear_create(&sub, &sh.child);
+            if (rc != KUDNN_B200_OK) {
+                return rc;
+            }
+            sh.child->forced_kernel = h->forced_kernel;
+        }
+        h->shard_mode = mode;
+        h->shard_count = nshards;
+    }
+    // one host thread per shard: set the device, stage, run, copy back
+    std::vector<int> codes(nshards, KUDNN_B200_OK);
+    std::vector<std::string> messages(nshards);
+    auto work = [&](int i) {
+        Handle::Shard &sh = h->shards[i];
+        if (sh.count == 0) {
+            return;
+        }
+        auto give_up = [&](int rc) {
+            codes[i] = rc;
+            messages[i] = g_error;
+        };
+        if (cudaSetDevice(sh.device) != cudaSuccess) {
+            give_up(fail(KUDNN_B200_CUDA_ERROR, "run_sharded: cannot select device %d", sh.device));
+            return;
+        }
+        const size_t es_b = kb::dtype_size(d.b_dtype);
+        // the child's weights: the whole matrix (row shards) or its slab of columns, packed once per weight pointer
+        const char *b_sub = static_cast<const char *>(args->b) + (cols ? sh.begin * d.b_sn * es_b : 0);
+        if (sh.weights != b_sub) {
+            int rc = kudnn_b200_linear_prepack(sh.child, b_sub, nullptr);
+            if (rc != KUDNN_B200_OK) {
+                give_up(rc);
+                return;
+            }
+            sh.weights = b_sub;
+        }
+        kudnn_b200_linear_args sub = *args;
+        sub.b = b_sub;
+        if (!cols) {
+            const long long r0 = sh.begin;
+            sub.a = static_cast<const char *>(args->a) + r0 * d.a_sm * kb::dtype_size(d.a_dtype);
+            sub.c = args->c != nullptr ? static_cast<char *>(args->c) + r0 * d.c_sm * kb::dtype_size(d.c_dtype) : nullptr;
+            sub.bias = d.has_bias ? static_cast<const char *>(args->bias) + r0 * d.bias_sm * kb::dtype_size(d.bias_dtype) : nullptr;
+            sub.res = has_res ? static_cast<const char *>(args->res) + r0 * d.res_sm * kb::dtype_size(d.res_dtype) : nullptr;
+            sub.out = has_res ? static_cast<char *>(args->out) + r0 * d.out_sm * kb::dtype_size(d.out_dtype) : nullptr;
+            int rc = kudnn_b200_linear_run_host(sh.child, &sub);
+            if (rc != KUDNN_B200_OK) {
+                give_up(rc);
+            }
+            return;
+        }
+        // column shard: x whole, the slabs of bias / res in, the slabs of c / out back, as strided copies
+        const long long c0 = sh.begin, nl = sh.count;
+        const size_t es_a = kb::dtype_size(d.a_dtype), es_c = kb::dtype_size(d.c_dtype), es_bias = kb::dtype_size(d.bias_dtype);
+        const size_t es_r = kb::dtype_size(d.res_dtype), es_o = kb::dtype_size(d.out_dtype);
+        cudaError_t e = sh.buf[0].reserve(static_cast<size_t>(d.m) * d.k * es_a);
+        if (e == cudaSuccess && d.has_bias) e = sh.buf[1].reserve(static_cast<size_t>(nl) * es_bias);
+        if (e == cudaSuccess && args->c != nullptr) e = sh.buf[2].reserve(static_cast<size_t>(d.m) * nl * es_c);
+        if (e == cudaSuccess && has_res) e = sh.buf[3].reserve(static_cast<size_t>(d.m) * nl * es_r);
+        if (e == cudaSuccess && has_res) e = sh.buf[4].reserve(static_cast<size_t>(d.m) * nl * es_o);
+        cudaStream_t st = nullptr;
+        if (e == cudaSuccess) {
+            e = cudaMemcpy2DAsync(sh.buf[0].ptr, d.k * es_a, args->a, d.a_sm * es_a, d.k * es_a, d.m, cudaMemcpyHostToDevice, st);
+        }
+        if (e == cudaSuccess && d.has_bias) {
+            e = cudaMemcpyAsync(sh.buf[1].ptr, static_cast<const char *>(args->bias) + c0 * d.bias_sn * es_bias, nl * es_bias,
+                                cudaMemcpyHostToDevice, st);
+        }
+        if (e == cudaSuccess && has_res) {
+            e = cudaMemcpy2DAsync(sh.buf[3].ptr, nl * es_r, static_cast<const char *>(args->res) + c0 * es_r, d.res_sm * es_r,
+                                  nl * es_r, d.m, cudaMemcpyHostToDevice, st);
+        }
+        if (e != cudaSuccess) {
+            give_up(fail_cuda(e, "run_sharded: staging"));
+            return;
+        }
+        sub.a = sh.buf[0].ptr;
+        sub.bias = d.has_bias ? sh.buf[1].ptr : nullptr;
+        sub.c = args->c != nullptr ? sh.buf[2].ptr : nullptr;
+        sub.res = has_res ? sh.buf[3].ptr : nullptr;
+        sub.out = has_res ? sh.buf[4].ptr : nullptr;
+        int rc = kudnn_b200_linear_run(sh.child, &sub, st);
+        if (rc != KUDNN_B200_OK) {
+            give_up(rc);
+            return;
+        }
+        if (args->c != nullptr) {
+            e = cudaMemcpy2DAsync(static_cast<char *>(args->c) + c0 * es_c, d.c_sm * es_c, sh.buf[2].ptr, nl * es_c, nl * es_c, d.m,
+                                  cudaMemcpyDeviceToHost, st);
+        }
+        if (e == cudaSuccess && has_res) {
+            e = cudaMemcpy2DAsync(static_cast<char *>(args->out) + c0 * es_o, d.out_sm * es_o, sh.buf[4].ptr, nl * es_o, nl * es_o,
+                                  d.m, cudaMemcpyDeviceToHost, st);
+        }
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) {
+            give_up(fail_cuda(e, "run_sharded: copy back"));
+            return;
+        }
+        rc = kudnn_b200_linear_check(sh.child, st);
+        if (rc != KUDNN_B200_OK) {
+            give_up(rc);
+        }
+    };
+    int cur = -1;
+    (void)cudaGetDevice(&cur);
+    std::vector<std::thread> threads;
+    for (int i = 1; i < nshards; ++i) {
+        threads.emplace_back(work, i);
+    }
+    work(0);
+    for (auto &t : threads) {
+        t.join();
+    }
+    if (cur >= 0) {
+        cudaSetDevice(cur);
+    }
+    int launches = 0;
+    for (int i = 0; i < nshards; ++i) {
+        if (codes[i] != KUDNN_B200_OK) {
+            return fail(codes[i], "shard %d: %s", i, messages[i].c_str());
+        }
+        if (h->shards[i].child != nullptr) {
+            launches += h->shards[i].child->last_launches;
+            h->last_kernel = h->shards[i].child->last_kernel;
+        }
+    }
+    h->last_launches = launches;
+    return KUDNN_B200_OK;
 }
 
 int kudnn_b200_linear_run_any(kudnn_b200_linear_t h, const kudnn_b200_linear_args *args, void *cuda_stream)

@@ -21,11 +21,21 @@ __device__ __forceinline__ void store_converted(void *dst, int dtype, long long 
 }
 
 // 32 x 32 tile through shared memory so both the strided read and the K-major write are coalesced
-__global__ void __launch_bounds__(256) pack_kmajor_kernel(const void *src, int src_dtype, long long rows, long long k,
-                                                          long long s_row, long long s_k, void *dst, int dst_dtype,
-                                                          long long ldd, long long k_pad)
+// blockIdx.z = flat batch index: the source matrix of a batch entry starts at the element offset its three batch
+// strides give, the packed one at flat * dst_batch elements
+__device__ __forceinline__ long long src_batch_offset(const PackBatch &pb, long long flat)
+{
+    const long long i2 = flat % pb.n2, r = flat / pb.n2;
+    return (r / pb.n1) * pb.sb[0] + (r % pb.n1) * pb.sb[1] + i2 * pb.sb[2];
+}
+
+__global__ void __launch_bounds__(256) pack_kmajor_kernel(const void *src_base, int src_dtype, long long rows, long long k,
+                                                          long long s_row, long long s_k, void *dst_base, int dst_dtype,
+                                                          long long ldd, long long k_pad, const PackBatch pb)
 {
     __shared__ float tile[32][33];
+    const void *src = static_cast<const char *>(src_base) + src_batch_offset(pb, blockIdx.z) * dtype_size(src_dtype);
+    void *dst = static_cast<char *>(dst_base) + static_cast<long long>(blockIdx.z) * pb.dst_batch * dtype_size(dst_dtype);
     const long long r0 = static_cast<long long>(blockIdx.x) * 32;
     const long long k0 = static_cast<long long>(blockIdx.y) * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -61,11 +71,13 @@ __device__ __forceinline__ float to_tf32(float x)
 }
 
 // dst row (pitch ldd floats) starts with three planes of k_pad floats.  Activations: [lo | hi | hi]; weights: [hi | lo | hi].
-__global__ void __launch_bounds__(256) split_tf32_kernel(const float *src, long long rows, long long k, long long s_row,
-                                                         long long s_k, float *dst, long long ldd, long long k_pad,
-                                                         int is_weight)
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float *src_base, long long rows, long long k, long long s_row,
+                                                         long long s_k, float *dst_base, long long ldd, long long k_pad,
+                                                         int is_weight, const PackBatch pb)
 {
     __shared__ float tile[32][33];
+    const float *src = src_base + src_batch_offset(pb, blockIdx.z);
+    float *dst = dst_base + static_cast<long long>(blockIdx.z) * pb.dst_batch;
     const long long r0 = static_cast<long long>(blockIdx.x) * 32;
     const long long k0 = static_cast<long long>(blockIdx.y) * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -142,25 +154,29 @@ cudaError_t launch_pack_blocks(const void *src, long long rows, long long k, lon
 
 cudaError_t launch_pack_kmajor(const void *src, int src_dtype, long long rows, long long k, long long s_row,
                                long long s_k, void *dst, int dst_dtype, long long ldd, long long k_pad,
-                               cudaStream_t stream)
+                               cudaStream_t stream, const PackBatch *batch)
 {
-    dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>((k_pad + 31) / 32));
-    if (grid.y > 65535) {
+    const PackBatch one = {1, 1, 1, {0, 0, 0}, 0};
+    const PackBatch &pb = batch != nullptr ? *batch : one;
+    dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>((k_pad + 31) / 32), static_cast<unsigned>(pb.count));
+    if (grid.y > 65535 || pb.count > 65535) {
         return cudaErrorInvalidValue;
     }
-    pack_kmajor_kernel<<<grid, 256, 0, stream>>>(src, src_dtype, rows, k, s_row, s_k, dst, dst_dtype, ldd, k_pad);
+    pack_kmajor_kernel<<<grid, 256, 0, stream>>>(src, src_dtype, rows, k, s_row, s_k, dst, dst_dtype, ldd, k_pad, pb);
     return cudaGetLastError();
 }
 
 cudaError_t launch_split_tf32(const void *src, long long rows, long long k, long long s_row, long long s_k, float *dst,
-                              long long ldd, long long k_pad, int is_weight, cudaStream_t stream)
+                              long long ldd, long long k_pad, int is_weight, cudaStream_t stream, const PackBatch *batch)
 {
-    dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>((k_pad + 31) / 32));
-    if (grid.y > 65535) {
+    const PackBatch one = {1, 1, 1, {0, 0, 0}, 0};
+    const PackBatch &pb = batch != nullptr ? *batch : one;
+    dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>((k_pad + 31) / 32), static_cast<unsigned>(pb.count));
+    if (grid.y > 65535 || pb.count > 65535) {
         return cudaErrorInvalidValue;
     }
     split_tf32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float *>(src), rows, k, s_row, s_k, dst, ldd, k_pad,
-                                                is_weight);
+                                                is_weight, pb);
     return cudaGetLastError();
 }
 

@@ -86,6 +86,16 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *t
         : "memory");
 }
 
+// the same with a third coordinate (batch entry); the box is one entry deep
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *tmap, uint64_t *bar, int x, int y, int z)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 // ---- CTA pair (cluster of two, tcgen05 cta_group::2) -----------------------------------------------------------
 // Address of the same shared-memory location in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_smem_addr, uint32_t rank)

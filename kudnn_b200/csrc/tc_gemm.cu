@@ -68,6 +68,11 @@ struct TcParams {
     // so that a last wave that would keep fewer than half the pairs busy is spread over twice as many
     int num_items, narrow_from;
     unsigned idesc_narrow;
+    // Batched problems: `batch` matrices share the launch, work items run over (batch entry, tile, split).  The tensor
+    // maps are then three-dimensional; an operand every entry shares (a_bz / b_bz = 0) is always read at entry 0.  The
+    // epilogue tensors are addressed through the batch strides in bp.
+    int batch, a_bz, b_bz;
+    BatchParams bp;
     long long wait_limit;  // SM cycles after which a wait on an mbarrier gives up
     // Test hook for the timeout path: the producer of CTA 0 leaves out the loads of this k-block of its first work
     // item (-1 = never), so the MMA thread's wait for that stage runs into wait_limit.  Nothing faults or hangs.
@@ -825,10 +830,16 @@ __device__ __forceinline__ void finish_split_rows(const EpiParams &e, const floa
 
 // Work item -> tile index, column offset inside the tile and width of the piece.
 template <bool kPair, int kBN>
-__device__ __forceinline__ void decode_item(const TcParams &p, int item, int &tile, int &n_off, int &width)
+__device__ __forceinline__ void decode_item(const TcParams &p, int item, int &tile, int &n_off, int &width, int &batch,
+                                            int &split)
 {
+    batch = 0;
+    split = 0;
     if (!kPair) {
-        tile = item / p.splits;
+        const int unit = item / p.splits;  // (batch entry, tile)
+        split = item - unit * p.splits;
+        batch = unit / p.num_tiles;
+        tile = unit - batch * p.num_tiles;
         n_off = 0;
         width = kBN;
     } else if (item < p.narrow_from) {
@@ -922,9 +933,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             uint32_t phase = 0;
             bool alive = true;
             for (int item = first_item; alive && item < p.num_items; item += item_stride) {
-                int tile, n_off, width;
-                decode_item<kPair, kBN>(p, item, tile, n_off, width);
-                const int split = kPair ? 0 : item - tile * p.splits;
+                int tile, n_off, width, batch, split;
+                decode_item<kPair, kBN>(p, item, tile, n_off, width, batch, split);
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
                 const int per_group = p.group_m * p.tiles_n;
@@ -957,8 +967,13 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                                          tn * kBN + n_off + static_cast<int>(pair_rank) * (width / 2));
                     } else {
                         mbar_expect_tx(full_bar + stage, kStageBytes);
-                        tma_load_2d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM);
-                        tma_load_2d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN);
+                        if (p.batch > 1) {
+                            tma_load_3d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM, p.a_bz != 0 ? batch : 0);
+                            tma_load_3d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN, p.b_bz != 0 ? batch : 0);
+                        } else {
+                            tma_load_2d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM);
+                            tma_load_2d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN);
+                        }
                     }
                     if (++stage == kStages) {
                         stage = 0;
@@ -976,9 +991,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             uint32_t acc_phase = 0;
             bool alive = true;
             for (int item = first_item; alive && item < p.num_items; item += item_stride) {
-                int tile, n_off, width;
-                decode_item<kPair, kBN>(p, item, tile, n_off, width);
-                const int split = kPair ? 0 : item - tile * p.splits;
+                int tile, n_off, width, batch, split;
+                decode_item<kPair, kBN>(p, item, tile, n_off, width, batch, split);
                 const uint32_t idesc = (width == kBN) ? p.idesc : p.idesc_narrow;
                 const int kb_begin = split * p.kb_per_split;
                 const int kb_end = (kb_begin + p.kb_per_split < p.num_kb) ? kb_begin + p.kb_per_split : p.num_kb;
@@ -1037,11 +1051,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: [32 * quarter, 32 * quarter + 32)
         const int row_in_tile = quarter * 32 + lane;
         const int part = (warp - 2) / 4;  // warps sharing a quarter split the tile's columns between them
-        const EpiParams &e = p.epi;
+        EpiParams e_batch;  // the epilogue tensors of the current batch entry (batched launches only)
         float *warp_bias = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + 256) + (warp - 2) * kWarpBiasFloats;
         // Rows are collected into 128-byte pieces before they are stored only when peers receive copies: for local
         // memory alone the 16-byte stores straight from registers are faster (measured both ways).
-        unsigned char *warp_stage = e.n_mirrors > 0 ? reinterpret_cast<unsigned char *>(bars) + kTailBytes +
+        unsigned char *warp_stage = p.epi.n_mirrors > 0 ? reinterpret_cast<unsigned char *>(bars) + kTailBytes +
                                                           (warp - 2) * kWarpStageBytes
                                                     : nullptr;
         int acc = 0;
@@ -1049,8 +1063,12 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         // "accumulator drained" goes to the MMA thread, which in a pair lives in the leader CTA
         const uint32_t tmem_empty_remote = kPair ? map_to_rank(smem_u32(tmem_empty), 0u) : 0u;
         for (int item = first_item; item < p.num_items; item += item_stride) {
-            int tile, n_off, width;
-            decode_item<kPair, kBN>(p, item, tile, n_off, width);
+            int tile, n_off, width, batch, split;
+            decode_item<kPair, kBN>(p, item, tile, n_off, width, batch, split);
+            if (p.batch > 1) {
+                e_batch = epi_for_batch(p.epi, p.bp, batch);
+            }
+            const EpiParams &e = p.batch > 1 ? e_batch : p.epi;
             const int per_group = p.group_m * p.tiles_n;
             const int group = tile / per_group;
             const int first_m = group * p.group_m;
@@ -1151,7 +1169,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         __syncwarp();
         cluster_sync_all();  // all partial tiles are in place (a hardware barrier over every thread of the cluster)
         if (warp >= 2 && *abort_flag == 0) {
-            const int tile = static_cast<int>(blockIdx.x) / p.splits;
+            const int unit = static_cast<int>(blockIdx.x) / p.splits;
+            const int batch = unit / p.num_tiles;
+            const int tile = unit - batch * p.num_tiles;
             const int per_group = p.group_m * p.tiles_n;
             const int group = tile / per_group;
             const int first_m = group * p.group_m;
@@ -1160,7 +1180,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const int tm = first_m + in_group % gsize;
             const int tn = in_group / gsize;
             const float *part = reinterpret_cast<const float *>(smem);
-            const EpiParams &e = p.epi;
+            EpiParams e_batch;
+            if (p.batch > 1) {
+                e_batch = epi_for_batch(p.epi, p.bp, batch);
+            }
+            const EpiParams &e = p.batch > 1 ? e_batch : p.epi;
             const uint32_t rank = cluster_rank();
             const int epi_tid = static_cast<int>(threadIdx.x) - 64;
             const bool typed = e.c_dtype == kKind && (e.has_bias == 0 || e.bias_dtype == kKind) &&
@@ -1239,8 +1263,26 @@ void resolve_encode()
 }
 
 cudaError_t encode_kmajor(CUtensorMap *map, const void *base, int kind, long long rows, long long k_total,
-                          long long ld_elems, int box_rows)
+                          long long ld_elems, int box_rows, long long batch = 1, long long batch_stride = 0)
 {
+    if (batch > 1) {
+        // [batch][rows][k]: a box is one batch entry deep.  An operand all entries share is encoded with one entry.
+        const int es3 = dtype_size(kind);
+        const CUtensorMapDataType dt3 = (kind == KUDNN_B200_F32)   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                        : (kind == KUDNN_B200_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                   : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        const bool shared = batch_stride == 0;
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(k_total), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(shared ? 1 : batch)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld_elems) * es3,
+                                 static_cast<cuuint64_t>(shared ? rows * ld_elems : batch_stride) * es3};
+        cuuint32_t box[3] = {static_cast<cuuint32_t>(kStageRowBytes / es3), static_cast<cuuint32_t>(box_rows), 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = g_encode(map, dt3, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+    }
     const int es = dtype_size(kind);
     const CUtensorMapDataType dt = (kind == KUDNN_B200_F32)   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : (kind == KUDNN_B200_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -1352,9 +1394,9 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
         return cudaErrorNotSupported;
     }
     const long long tiles_m = (m + kBM - 1) / kBM;
-    const long long tiles256 = tiles_m * ((n + 255) / 256);
+    const long long tiles256 = ops.batch * tiles_m * ((n + 255) / 256);
     const int bn = (tiles256 >= sm_count || n > 128 * 64) ? 256 : 128;
-    const long long tiles = tiles_m * ((n + bn - 1) / bn);
+    const long long tiles = ops.batch * tiles_m * ((n + bn - 1) / bn);  // over all batch entries
     if (tiles > (1ll << 30)) {
         return cudaErrorInvalidValue;
     }
@@ -1364,7 +1406,7 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     // pair / single CTA: 4096 rows 1.385 / 1.396, 8192 rows 2.84 / 2.85, 16384 rows 6.10 / 5.96, 32768 rows
     // 13.3 / 12.4).
     const double flops = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(ops.k_total);
-    bool pair = bn == 256 && m > kBM && flops < 6.0e12;
+    bool pair = bn == 256 && m > kBM && flops < 6.0e12 && ops.batch == 1;  // batched launches use single CTAs
     if (const char *env = std::getenv("KUDNN_B200_TC_PAIR")) {
         pair = pair && std::atoi(env) != 0;
     }
@@ -1419,11 +1461,11 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
         plan->narrow_from = static_cast<int>(narrow ? pair_tiles - rem : pair_tiles);
     }
     CUtensorMap ta, tb;
-    cudaError_t e = encode_kmajor(&ta, ops.a, ops.kind, m, ops.k_total, ops.lda, kBM);
+    cudaError_t e = encode_kmajor(&ta, ops.a, ops.kind, m, ops.k_total, ops.lda, kBM, ops.batch, ops.a_bstride);
     if (e != cudaSuccess) {
         return e;
     }
-    e = encode_kmajor(&tb, ops.b, ops.kind, n, ops.k_total, ops.ldb, b_rows);
+    e = encode_kmajor(&tb, ops.b, ops.kind, n, ops.k_total, ops.ldb, b_rows, ops.batch, ops.b_bstride);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1433,10 +1475,22 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
 }
 
 cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams &epi, long long m, long long n,
-                      DeviceStatus *status, cudaStream_t stream, long long wait_limit_cycles, int skip_kblock)
+                      DeviceStatus *status, cudaStream_t stream, long long wait_limit_cycles, int skip_kblock,
+                      const BatchParams *bp)
 {
     TcParams p;
     p.epi = epi;
+    p.batch = static_cast<int>(ops.batch);
+    p.a_bz = ops.a_bstride != 0 ? 1 : 0;
+    p.b_bz = ops.b_bstride != 0 ? 1 : 0;
+    std::memset(&p.bp, 0, sizeof(p.bp));
+    p.bp.n1 = p.bp.n2 = 1;
+    if (ops.batch > 1) {
+        if (bp == nullptr || plan.pair != 0) {
+            return cudaErrorInvalidValue;
+        }
+        p.bp = *bp;
+    }
     p.wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : kDefaultWaitLimitCycles;
     // the test hook is honoured by the plain single-CTA shape only (no cluster partner is left half-signalled)
     p.skip_kb = (plan.pair == 0 && plan.splits == 1) ? skip_kblock : -1;
@@ -1462,7 +1516,8 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
         gm = gm < 2 ? 2 : (gm > kMaxGroupM ? kMaxGroupM : gm);
         p.group_m = static_cast<int>(gm);
     }
-    p.num_items = plan.pair ? plan.narrow_from + 2 * (p.num_tiles - plan.narrow_from) : p.num_tiles * plan.splits;
+    p.num_items = plan.pair ? plan.narrow_from + 2 * (p.num_tiles - plan.narrow_from)
+                            : p.num_tiles * plan.splits * static_cast<int>(ops.batch);
     p.narrow_from = plan.pair ? plan.narrow_from : p.num_tiles;
     p.idesc_narrow = make_idesc(ops.kind, plan.block_n / 2, plan.pair ? 2 * kBM : kBM);
     if (plan.pair) {

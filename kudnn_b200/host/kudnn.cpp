@@ -648,10 +648,17 @@ public:
         args.alpha = alpha;
         args.beta = beta;
         args.gamma = gamma;
-        const int rc = kudnn_b200_linear_run_any(handle_, &args, stream_);
+        const int rc = shards_ > 0 ? kudnn_b200_linear_run_sharded(handle_, &args, shards_,
+                                                                  shardColumns_ ? KUDNN_B200_SHARD_COLS : KUDNN_B200_SHARD_ROWS)
+                                   : kudnn_b200_linear_run_any(handle_, &args, stream_);
         if (rc != KUDNN_B200_OK) {
             ThrowCabi(rc, who_);
         }
+    }
+    void SetSharding(int shards, bool byColumns) noexcept
+    {
+        shards_ = shards;
+        shardColumns_ = byColumns;
     }
 
     void Prepack(const void *b) const
@@ -673,6 +680,8 @@ private:
     bool hasBias_;
     const char *who_;
     void *stream_ = nullptr;
+    int shards_ = 0;
+    bool shardColumns_ = false;
 };
 
 }  // namespace Detail
@@ -770,6 +779,10 @@ void Gemm::PrepackWeights(const void *b) const noexcept(false)
 void Gemm::SetStream(void *cudaStream) noexcept
 {
     pImpl->SetStream(cudaStream);
+}
+void Gemm::SetSharding(int shards, bool byColumns) noexcept
+{
+    pImpl->SetSharding(shards, byColumns);
 }
 int Gemm::LastKernel() const noexcept
 {

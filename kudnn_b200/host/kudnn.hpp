@@ -490,6 +490,9 @@ public:
     void PrepackWeights(const void *b) const noexcept(false);  // pack once; later Run(.., b, ..) reuses the packed copy
     void SetStream(void *cudaStream) noexcept;                 // stream for device-pointer runs (default: stream 0)
     int LastKernel() const noexcept;                           // KUDNN_B200_KERNEL_* of the most recent Run
+    // Host-pointer runs are split over this machine's GPUs from now on: `shards` pieces of the rows (byColumns =
+    // false) or of the columns of the layer, shard i on device i modulo the device count.  0 switches it off.
+    void SetSharding(int shards, bool byColumns = false) noexcept;
 
 private:
     std::unique_ptr<Detail::LinearCore> pImpl;

@@ -251,6 +251,36 @@ def test_tc_cta_pairs(cuda_device, dtype, m, n, k):
     helpers.parity(case, cuda_device, kernel=kb.KERNEL_TC, acc=ko.ACC_F64, expect_kernel=kb.KERNEL_TC)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("batch,a_bcast,b_bcast", [((2,), False, False), ((3, 2), False, False), ((4, 3, 2), False, False),
+                                                    ((2, 2), True, False), ((5,), False, True)])
+@pytest.mark.parametrize("a_layout,b_layout", [("AB", "BA"), ("AB", "AB"), ("BA", "AB")])
+def test_tc_batched(cuda_device, dtype, batch, a_bcast, b_bcast, a_layout, b_layout):
+    """Batched N-D Linear on the tensor-core kernel: the batch entry is a coordinate of its tile scheduler.  Per-batch
+    weights (the reference's 3-D to 5-D cases, linear_activation_gtest.cpp:475-512, N-major as its tests store them, or
+    K-major), one shared activation matrix, one shared weight matrix; operands that are not K-major are packed, all
+    batch entries in one launch."""
+    if b_bcast and (a_layout, b_layout) == ("AB", "BA"):
+        pytest.skip("shared K-major weights with row-major activations collapse into one 2-D problem (tested elsewhere)")
+    case = dict(m=130, n=264, k=136, dtype=dtype, bias="row", act=kb.ACT_RELU, act_alpha=0.0, res_op=kb.RES_IDENTICAL,
+                batch=batch, a_bcast=a_bcast, b_bcast=b_bcast, a_layout=a_layout, b_layout=b_layout, x_dist="normal",
+                w_std=0.05, seed=56)
+    helpers.parity(case, cuda_device, acc=ko.ACC_F64, expect_kernel=kb.KERNEL_TC)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_tc_batched_split_k_and_activations(cuda_device, dtype):
+    # few tiles and a long k in every batch entry: cluster split-K with a batch coordinate; general epilogue
+    case = dict(m=100, n=200, k=2056, dtype=dtype, bias="full", act=kb.ACT_GELU_ERF, batch=(3,), b_bcast=False,
+                x_dist="normal", w_std=0.02, seed=57)
+    helpers.parity(case, cuda_device, acc=ko.ACC_F64, expect_kernel=kb.KERNEL_TC)
+    # the reference's own batched shape class (110 x 20 . 20 x 200 per entry) is too small to be worth a tensor-core
+    # launch and stays on the general kernel
+    small = dict(m=110, n=200, k=20, dtype=dtype, bias="full", act=kb.ACT_RELU, act_alpha=0.0, batch=(4, 3, 2),
+                 b_bcast=False, b_layout="AB", seed=58)
+    helpers.parity(small, cuda_device, acc=ko.ACC_F64, expect_kernel=kb.KERNEL_SIMT)
+
+
 def test_tc_agrees_with_general_kernel(cuda_device):
     case = dict(m=512, n=768, k=512, dtype="bf16", bias="row", act=kb.ACT_SWISH, x_dist="normal", w_std=0.03, seed=47)
     desc, arrays, c = helpers.build_case(case)

@@ -38,6 +38,12 @@ extern "C" {
 #define KUDNN_B200_F32 1
 #define KUDNN_B200_F16 2
 #define KUDNN_B200_BF16 3
+/* Integer types, accepted in two families of the reference's table (src/dnn/src/kudnn_gemm.cpp:590-601):
+ *   a, b in {S8, U8}, c and bias S32 (:259-334): exact 32-bit integer sums, no activation, no second output;
+ *   a F16, b in {S8, U8}, c F16 (:336-372, "W8A16"): the weights are widened to fp16 when they are packed. */
+#define KUDNN_B200_S32 4
+#define KUDNN_B200_S8 5
+#define KUDNN_B200_U8 6
 
 /* Activations: the values of KuDNN::ActivationFunction (src/dnn/include/operations/kudnn_eltwise.hpp:24-54);
  * 0 (UNIMPLEMENTED there) means "no activation" here. */

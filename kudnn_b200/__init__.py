@@ -7,7 +7,7 @@ sm_100 device is present, calls fail with an error.
 """
 from .capi import (  # noqa: F401
     ACT_GELU_ERF, ACT_GELU_TANH, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_TANH,
-    BF16, F16, F32,
+    BF16, F16, F32, S32, S8, U8,
     KERNEL_AUTO, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_SIMT, KERNEL_TC, KERNEL_NAMES,
     RES_ELTWISE_MUL, RES_EXT, RES_IDENTICAL, RES_NONE,
     KudnnError, Linear, LinearDesc, activation, debug_fail_allocation, library, library_path, make_desc, run_static_scratch, shard_range,
@@ -17,7 +17,7 @@ from .capi import (  # noqa: F401
 
 __all__ = [
     "ACT_GELU_ERF", "ACT_GELU_TANH", "ACT_NONE", "ACT_RELU", "ACT_SIGMOID", "ACT_SWISH", "ACT_TANH",
-    "BF16", "F16", "F32",
+    "BF16", "F16", "F32", "S32", "S8", "U8",
     "KERNEL_AUTO", "KERNEL_GEMV_FMA", "KERNEL_GEMV_MMA", "KERNEL_SIMT", "KERNEL_TC", "KERNEL_NAMES",
     "RES_ELTWISE_MUL", "RES_EXT", "RES_IDENTICAL", "RES_NONE",
     "KudnnError", "Linear", "LinearDesc", "activation", "debug_fail_allocation", "library", "library_path", "make_desc", "run_static_scratch", "shard_range",

@@ -6,7 +6,7 @@ this module never touches the data itself.
 import ctypes
 import os
 
-F32, F16, BF16 = 1, 2, 3
+F32, F16, BF16, S32, S8, U8 = 1, 2, 3, 4, 5, 6
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_SIGMOID, ACT_GELU_TANH, ACT_SWISH, ACT_GELU_ERF = 0, 5, 9, 10, 20, 25, 27
 RES_NONE, RES_EXT, RES_IDENTICAL, RES_ELTWISE_MUL = 0, 1, 2, 3
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_GEMV_FMA, KERNEL_GEMV_MMA, KERNEL_TC = 0, 1, 2, 3, 4
@@ -127,7 +127,7 @@ def _check(status):
 
 
 def make_desc(m, n, k, dtype, *, a_strides=None, b_strides=None, c_strides=None, has_bias=False, bias_strides=None,
-              bias_dtype=None, c_dtype=None, act=ACT_NONE, act_alpha=1.0, act_beta=0.0, res_op=RES_NONE,
+              bias_dtype=None, c_dtype=None, b_dtype=None, act=ACT_NONE, act_alpha=1.0, act_beta=0.0, res_op=RES_NONE,
               res_strides=None, out_strides=None, res_dtype=None, out_dtype=None, batch=(0, 0, 0), a_sb=(0, 0, 0),
               b_sb=(0, 0, 0), c_sb=(0, 0, 0), bias_sb=(0, 0, 0), res_sb=(0, 0, 0), out_sb=(0, 0, 0)):
     """Descriptor for c[m,n] = act(a[m,k] . b[k,n] + bias), out = c (+) res.
@@ -139,7 +139,8 @@ def make_desc(m, n, k, dtype, *, a_strides=None, b_strides=None, c_strides=None,
     d = LinearDesc()
     d.m, d.n, d.k = m, n, k
     d.batch[:] = batch
-    d.a_dtype = d.b_dtype = dtype
+    d.a_dtype = dtype
+    d.b_dtype = b_dtype or dtype
     d.c_dtype = c_dtype or dtype
     d.bias_dtype = bias_dtype or dtype
     d.res_dtype = res_dtype or (c_dtype or dtype)

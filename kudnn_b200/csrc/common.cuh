@@ -40,6 +40,9 @@ struct EpiParams {
     float alpha, beta, gamma, act_alpha;
     int c_dtype, bias_dtype, res_dtype, out_dtype;
     int has_bias, act, res_op;
+    // fp16 result of the <fp16, fp16, fp16, fp16> instance: rounded to fp16 before the bias is added in fp16.  Every
+    // other fp16 result (wider bias, 8-bit weights) adds the bias in fp32 and rounds once.
+    int half_chain;
     int m, n;
     // Mirrors: further copies of the outputs (same strides), e.g. the same tensor in every peer GPU's memory, written
     // by the same stores.  Byte distance of each mirror from c / out.
@@ -72,6 +75,15 @@ __device__ __forceinline__ float load_as_f32(const void *p, int dtype, long long
 {
     if (dtype == KUDNN_B200_F32) {
         return static_cast<const float *>(p)[idx];
+    }
+    if (dtype == KUDNN_B200_S8) {
+        return static_cast<float>(static_cast<const signed char *>(p)[idx]);
+    }
+    if (dtype == KUDNN_B200_U8) {
+        return static_cast<float>(static_cast<const unsigned char *>(p)[idx]);
+    }
+    if (dtype == KUDNN_B200_S32) {
+        return static_cast<float>(static_cast<const int *>(p)[idx]);
     }
     unsigned short h = static_cast<const unsigned short *>(p)[idx];
     return dtype == KUDNN_B200_F16 ? f16_bits_to_f32(h) : bf16_bits_to_f32(h);
@@ -202,7 +214,7 @@ __device__ __forceinline__ EpiResult finish_element(const EpiParams &p, float ac
         t += p.beta * c_old;
     }
     float c1;
-    if (ct == KUDNN_B200_F16 && (!p.has_bias || p.bias_dtype == KUDNN_B200_F16)) {
+    if (p.half_chain != 0) {
         c1 = round_rne(t, KUDNN_B200_F16);
         if (p.has_bias) {
             c1 = round_rne(c1 + bias, KUDNN_B200_F16);
@@ -292,7 +304,7 @@ __device__ __forceinline__ long long batch_offset(const long long sb[3], const l
 
 __host__ __device__ __forceinline__ int dtype_size(int dtype)
 {
-    return dtype == KUDNN_B200_F32 ? 4 : 2;
+    return (dtype == KUDNN_B200_F32 || dtype == KUDNN_B200_S32) ? 4 : ((dtype == KUDNN_B200_S8 || dtype == KUDNN_B200_U8) ? 1 : 2);
 }
 
 __device__ __forceinline__ void *offset_ptr(void *p, int dtype, long long elems)

@@ -45,6 +45,8 @@ struct GemvPlan {
 int set_last_error(int code, const char *message);
 
 cudaError_t launch_simt(const LinearProblem &pr, cudaStream_t stream);
+// 8-bit integer operands (S8 / U8), 32-bit integer result and bias: exact sums
+cudaError_t launch_int_gemm(const LinearProblem &pr, cudaStream_t stream);
 
 // Streaming kernels for m <= 16 (2-D problems, K-contiguous operands).
 bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPlan *plan);

@@ -41,6 +41,11 @@ bool is_float_dtype(int dt)
     return dt == KUDNN_B200_F32 || dt == KUDNN_B200_F16 || dt == KUDNN_B200_BF16;
 }
 
+bool is_int8_dtype(int dt)
+{
+    return dt == KUDNN_B200_S8 || dt == KUDNN_B200_U8;
+}
+
 long long batch_extent(const kudnn_b200_linear_desc &d, int i)
 {
     return d.batch[i] > 0 ? d.batch[i] : 1;
@@ -143,6 +148,7 @@ struct kudnn_b200_linear_s {
     DeviceBuffer b_scratch;     // per-call packed weights (when not pre-packed)
     DeviceBuffer b_packed;      // pre-packed weights
     DeviceBuffer b_blocked;     // decode-shaped handles: the weights once more in 8-row x 64-k blocks
+    DeviceBuffer q_scratch;     // 8-bit weights widened to fp16 per call (when not pre-packed)
     DeviceBuffer stage[6];      // host-pointer staging: a, b, c, bias, res, out
 
     // pre-pack state
@@ -248,6 +254,11 @@ void fill_epi(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, 
     e->res_dtype = d.res_dtype;
     e->out_dtype = d.out_dtype;
     e->has_bias = d.has_bias;
+    // d.reserved != 0: the weights of this (internal) descriptor were widened from 8 bits
+    e->half_chain = (d.c_dtype == KUDNN_B200_F16 && d.a_dtype == KUDNN_B200_F16 && d.b_dtype == KUDNN_B200_F16 &&
+                     d.reserved == 0 && (d.has_bias == 0 || d.bias_dtype == KUDNN_B200_F16))
+                        ? 1
+                        : 0;
     e->act = d.act;
     e->res_op = d.res_op;
     e->m = static_cast<int>(d.m);
@@ -337,7 +348,9 @@ int pack_weights(Handle *h, const void *b_dev, DeviceBuffer *buf, bool with_raw,
         if (e != cudaSuccess) {
             return fail_cuda(e, "packed weights");
         }
-        e = kb::launch_pack_kmajor(b_dev, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, buf->ptr, d.b_dtype, pitch, k_pad, stream);
+        // 8-bit weights are widened to fp16 here (exact), the type of the activations they meet
+        e = kb::launch_pack_kmajor(b_dev, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, buf->ptr,
+                                   is_int8_dtype(d.b_dtype) ? KUDNN_B200_F16 : d.b_dtype, pitch, k_pad, stream);
         if (e != cudaSuccess) {
             return fail_cuda(e, "weight pack kernel");
         }
@@ -416,6 +429,55 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
     int rc = ensure_device(h);
     if (rc != KUDNN_B200_OK) {
         return rc;
+    }
+
+    // ---- 8-bit integer product: exact 32-bit sums on the integer kernel
+    if (d.c_dtype == KUDNN_B200_S32) {
+        kb::LinearProblem ip;
+        fill_problem(d, args, &ip);
+        if (ip.batch_count > 65535) {
+            return fail(KUDNN_B200_UNSUPPORTED, "more than 65535 batch entries");
+        }
+        cudaError_t e = kb::launch_int_gemm(ip, stream);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "integer kernel launch");
+        }
+        h->last_kernel = KUDNN_B200_KERNEL_SIMT;
+        h->last_launches = 1;
+        return KUDNN_B200_OK;
+    }
+    // ---- fp16 activations with 8-bit weights: the weights are widened to fp16, K-major, once when they are pre-packed
+    // or else per call, and the problem continues as fp16 x fp16 whose fp16 result is rounded once
+    if (is_int8_dtype(d.b_dtype)) {
+        kudnn_b200_linear_desc dq = d;
+        dq.b_dtype = KUDNN_B200_F16;
+        dq.reserved = 1;
+        dq.b_sk = 1;
+        kudnn_b200_linear_args aq = args;
+        if (h->packed_key != nullptr && h->packed_key == args.b) {
+            dq.b_sn = h->packed_ld;  // the packed state stands for args.b: the inner call finds it by the same key
+        } else {
+            if (batch_extent(d, 0) * batch_extent(d, 1) * batch_extent(d, 2) != 1) {
+                return fail(KUDNN_B200_UNSUPPORTED, "8-bit weights of batched problems are not supported");
+            }
+            const long long k_pad = round_up(d.k, 8);
+            cudaError_t e = h->q_scratch.reserve(static_cast<size_t>(d.n) * k_pad * 2);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "widened weights");
+            }
+            e = kb::launch_pack_kmajor(args.b, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, h->q_scratch.ptr, KUDNN_B200_F16, k_pad, k_pad,
+                                       stream);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "weight widening kernel");
+            }
+            dq.b_sn = k_pad;
+            aq.b = h->q_scratch.ptr;
+        }
+        const int rcq = run_device(h, dq, aq, stream);
+        if (rcq == KUDNN_B200_OK && aq.b != args.b) {
+            h->last_launches += 1;
+        }
+        return rcq;
     }
 
     kb::LinearProblem pr;
@@ -889,10 +951,17 @@ int kudnn_b200_linear_validate(const kudnn_b200_linear_desc *desc)
             return fail(KUDNN_B200_BAD_ARGUMENTS, "validate: negative batch extent");
         }
     }
-    if (!is_float_dtype(d.a_dtype) || !is_float_dtype(d.b_dtype) || !is_float_dtype(d.c_dtype)) {
-        return fail(KUDNN_B200_UNSUPPORTED, "validate: only F32 / F16 / BF16 operands are implemented");
+    const bool int_gemm = is_int8_dtype(d.a_dtype) && is_int8_dtype(d.b_dtype) && d.c_dtype == KUDNN_B200_S32;
+    const bool w8a16 = d.a_dtype == KUDNN_B200_F16 && is_int8_dtype(d.b_dtype) && d.c_dtype == KUDNN_B200_F16;
+    if (int_gemm) {
+        // <s8|u8, s8|u8, s32, s32> (src/dnn/src/kudnn_gemm.cpp:259-334): a plain product with an optional s32 bias
+        if ((d.has_bias != 0 && d.bias_dtype != KUDNN_B200_S32) || d.act != KUDNN_B200_ACT_NONE || d.res_op != KUDNN_B200_RES_NONE) {
+            return fail(KUDNN_B200_UNSUPPORTED, "validate: 8-bit integer products take an S32 bias and no post-operation");
+        }
+    } else if (!is_float_dtype(d.a_dtype) || !(is_float_dtype(d.b_dtype) || w8a16) || !is_float_dtype(d.c_dtype)) {
+        return fail(KUDNN_B200_UNSUPPORTED, "validate: operands must be F32 / F16 / BF16, or F16 x S8/U8 -> F16, or S8/U8 x S8/U8 -> S32");
     }
-    if (d.has_bias != 0 && !is_float_dtype(d.bias_dtype)) {
+    if (!int_gemm && d.has_bias != 0 && !is_float_dtype(d.bias_dtype)) {
         return fail(KUDNN_B200_UNSUPPORTED, "validate: bias type");
     }
     switch (d.act) {
@@ -1007,6 +1076,7 @@ int kudnn_b200_linear_destroy(kudnn_b200_linear_t h)
         h->b_scratch.release();
         h->b_packed.release();
         h->b_blocked.release();
+        h->q_scratch.release();
         for (auto &s : h->stage) {
             s.release();
         }
@@ -1064,7 +1134,10 @@ int kudnn_b200_linear_prepack(kudnn_b200_linear_t h, const void *b, void *cuda_s
         b_dev = h->stage[1].ptr;
     }
     h->plan_valid = false;
-    if (on_device && d.b_dtype != KUDNN_B200_F32 && kmajor_ready(b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
+    if (d.c_dtype == KUDNN_B200_S32) {
+        return KUDNN_B200_OK;  // the integer kernel reads the weights as they are: nothing to pack
+    }
+    if (on_device && d.b_dtype != KUDNN_B200_F32 && !is_int8_dtype(d.b_dtype) && kmajor_ready(b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
         // already in the streamed layout: the packed copy is the caller's buffer itself
         h->b_packed.release();
         h->packed_ptr = b;
@@ -1088,7 +1161,8 @@ int kudnn_b200_linear_prepack(kudnn_b200_linear_t h, const void *b, void *cuda_s
     // second copy in blocks of 8 rows x 64 k, the unit their MMA kernels read, so that a warp's loads are one
     // contiguous piece of memory.  A single activation row stays on the FMA kernel, which reads plain rows.
     h->blocked_kpad = 0;
-    if (d.m >= 2 && d.m <= 16 && d.b_dtype != KUDNN_B200_F32 && d.a_dtype == d.b_dtype && d.k % 8 == 0) {
+    if (d.m >= 2 && d.m <= 16 && d.b_dtype != KUDNN_B200_F32 &&
+        (d.a_dtype == d.b_dtype || (d.a_dtype == KUDNN_B200_F16 && is_int8_dtype(d.b_dtype))) && d.k % 8 == 0) {
         const long long k_pad = round_up(d.k, 256);
         e = h->b_blocked.reserve(static_cast<size_t>(round_up(d.n, 8)) * k_pad * 2);
         if (e != cudaSuccess) {

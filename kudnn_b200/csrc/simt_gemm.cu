@@ -1,5 +1,7 @@
 // General Linear kernel: any element strides, any of the three float storage types per tensor, any size,
-// leading batch dimensions with broadcast.  fp32 FMA accumulation in ascending k.  It covers the shapes the
+// leading batch dimensions with broadcast.  fp32 FMA accumulation in ascending k.  The same kernel with 32-bit integer
+// accumulators is the 8-bit integer product <s8|u8, s8|u8, s32, s32> of the reference
+// (src/dnn/src/kudnn_gemm.cpp:259-334): exact sums, an optional s32 bias, no post-operation.  It covers the shapes the
 // tensor-core and streaming kernels decline (rows that are not 16-byte aligned, tiny problems, transposed
 // activations) and serves as the on-device cross-check of the fast kernels.
 //
@@ -25,10 +27,41 @@ struct SimtParams {
     BatchParams batch;
 };
 
+__device__ __forceinline__ int load_as_int(const void *p, int dtype, long long idx)
+{
+    return dtype == KUDNN_B200_S8 ? static_cast<int>(static_cast<const signed char *>(p)[idx])
+                                  : static_cast<int>(static_cast<const unsigned char *>(p)[idx]);
+}
+
+// c = alpha * acc + beta * c_old + bias for 32-bit integer results.  With alpha = 1 and beta = 0 or 1 (what the
+// reference's callers use) everything stays in integers; other scalars go through fp64 and round to nearest.
+__device__ __forceinline__ void epilogue_int(const EpiParams &p, int acc, long long mi, long long ni)
+{
+    int *c = static_cast<int *>(p.c);
+    const long long ic = mi * p.c_sm + ni * p.c_sn;
+    long long r = acc;
+    if (p.alpha != 1.0f || (p.beta != 0.0f && p.beta != 1.0f)) {
+        double t = static_cast<double>(p.alpha) * acc;
+        if (p.beta != 0.0f) {
+            t += static_cast<double>(p.beta) * c[ic];
+        }
+        r = llrint(t);
+    } else if (p.beta == 1.0f) {
+        r += c[ic];
+    }
+    if (p.has_bias) {
+        r += static_cast<const int *>(p.bias)[mi * p.bias_sm + ni * p.bias_sn];
+    }
+    r = r > 2147483647ll ? 2147483647ll : (r < -2147483648ll ? -2147483648ll : r);
+    c[ic] = static_cast<int>(r);
+}
+
+template <typename T>
 __global__ void __launch_bounds__(256) simt_linear_kernel(const SimtParams p)
 {
-    __shared__ float sa[kStepK][kTile + 4];
-    __shared__ float sb[kStepK][kTile + 4];
+    constexpr bool kInt = sizeof(T) == sizeof(int) && T(1) / T(2) == T(0);
+    __shared__ T sa[kStepK][kTile + 4];
+    __shared__ T sb[kStepK][kTile + 4];
 
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;
@@ -41,12 +74,12 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(const SimtParams p)
     const void *b = offset_ptr(p.b, p.b_dtype, batch_offset(p.batch.b_sb, bidx));
     const EpiParams epi = epi_for_batch(p.epi, p.batch, blockIdx.z);
 
-    float acc[4][4];
+    T acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            acc[i][j] = 0.0f;
+            acc[i][j] = T(0);
         }
     }
 
@@ -61,9 +94,10 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(const SimtParams p)
                 r = e % kTile;
                 kk = e / kTile;
             }
-            float v = 0.0f;
+            T v = T(0);
             if (m0 + r < p.m && k0 + kk < p.k) {
-                v = load_as_f32(a, p.a_dtype, (m0 + r) * p.a_sm + static_cast<long long>(k0 + kk) * p.a_sk);
+                const long long idx = (m0 + r) * p.a_sm + static_cast<long long>(k0 + kk) * p.a_sk;
+                v = kInt ? static_cast<T>(load_as_int(a, p.a_dtype, idx)) : static_cast<T>(load_as_f32(a, p.a_dtype, idx));
             }
             sa[kk][r] = v;
         }
@@ -76,16 +110,17 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(const SimtParams p)
                 c = e % kTile;
                 kk = e / kTile;
             }
-            float v = 0.0f;
+            T v = T(0);
             if (n0 + c < p.n && k0 + kk < p.k) {
-                v = load_as_f32(b, p.b_dtype, (n0 + c) * p.b_sn + static_cast<long long>(k0 + kk) * p.b_sk);
+                const long long idx = (n0 + c) * p.b_sn + static_cast<long long>(k0 + kk) * p.b_sk;
+                v = kInt ? static_cast<T>(load_as_int(b, p.b_dtype, idx)) : static_cast<T>(load_as_f32(b, p.b_dtype, idx));
             }
             sb[kk][c] = v;
         }
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < kStepK; ++kk) {
-            float av[4], bv[4];
+            T av[4], bv[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 av[i] = sa[kk][ty * 4 + i];
@@ -95,7 +130,7 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(const SimtParams p)
             for (int i = 0; i < 4; ++i) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                    acc[i][j] = kInt ? acc[i][j] + av[i] * bv[j] : static_cast<T>(fmaf(av[i], bv[j], acc[i][j]));
                 }
             }
         }
@@ -112,7 +147,11 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(const SimtParams p)
         for (int j = 0; j < 4; ++j) {
             const long long ni = n0 + tx * 4 + j;
             if (ni < p.n) {
-                epilogue_scalar(epi, acc[i][j], mi, ni);
+                if (kInt) {
+                    epilogue_int(epi, static_cast<int>(acc[i][j]), mi, ni);
+                } else {
+                    epilogue_scalar(epi, static_cast<float>(acc[i][j]), mi, ni);
+                }
             }
         }
     }
@@ -120,7 +159,19 @@ __global__ void __launch_bounds__(256) simt_linear_kernel(const SimtParams p)
 
 }  // namespace
 
+static cudaError_t launch_general(const LinearProblem &pr, cudaStream_t stream, bool integer);
+
 cudaError_t launch_simt(const LinearProblem &pr, cudaStream_t stream)
+{
+    return launch_general(pr, stream, false);
+}
+
+cudaError_t launch_int_gemm(const LinearProblem &pr, cudaStream_t stream)
+{
+    return launch_general(pr, stream, true);
+}
+
+static cudaError_t launch_general(const LinearProblem &pr, cudaStream_t stream, bool integer)
 {
     SimtParams p;
     p.a = pr.a;
@@ -149,7 +200,11 @@ cudaError_t launch_simt(const LinearProblem &pr, cudaStream_t stream)
         if (grid.y > 65535) {
             return cudaErrorInvalidValue;
         }
-        simt_linear_kernel<<<grid, 256, 0, stream>>>(p);
+        if (integer) {
+            simt_linear_kernel<int><<<grid, 256, 0, stream>>>(p);
+        } else {
+            simt_linear_kernel<float><<<grid, 256, 0, stream>>>(p);
+        }
     }
     return cudaGetLastError();
 }

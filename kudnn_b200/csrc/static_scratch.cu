@@ -153,6 +153,10 @@ extern "C" int kudnn_b200_linear_run_static_scratch(const kudnn_b200_linear_desc
     e.res_dtype = d.res_dtype;
     e.out_dtype = d.out_dtype;
     e.has_bias = d.has_bias;
+    e.half_chain = (d.c_dtype == KUDNN_B200_F16 && d.a_dtype == KUDNN_B200_F16 && d.b_dtype == KUDNN_B200_F16 &&
+                    (d.has_bias == 0 || d.bias_dtype == KUDNN_B200_F16))
+                       ? 1
+                       : 0;
     e.act = d.act;
     e.res_op = d.res_op;
     e.n_mirrors = 0;

@@ -198,7 +198,7 @@ __device__ __forceinline__ void epilogue_group8(const EpiParams &e, const uint32
         const long long ib = mi * e.bias_sm + ni * e.bias_sn;
         load8(e.bias, e.bias_dtype, ib, e.bias_sn, full8 && vec_ok(e.bias, e.bias_dtype, ib, e.bias_sn), valid, side);
     }
-    if (ct == KUDNN_B200_F16 && (!e.has_bias || e.bias_dtype == KUDNN_B200_F16)) {
+    if (e.half_chain != 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             v[j] = __half2float(__float2half_rn(v[j]));
@@ -416,7 +416,7 @@ __device__ __forceinline__ void compute_c8_fast(const EpiParams &e, const uint32
             side[j] = rp.bias_scalar;
         }
     }
-    if (ct == KUDNN_B200_F16 && (kDt > 0 || rp.bias_mode == 0 || e.bias_dtype == KUDNN_B200_F16)) {
+    if (ct == KUDNN_B200_F16 && e.half_chain != 0) {
         round_rne8<KUDNN_B200_F16>(v);
         if (rp.bias_mode != 0) {
 #pragma unroll

@@ -499,6 +499,12 @@ int DtypeCode(Element::TypeT t) noexcept
             return KUDNN_B200_F16;
         case Element::TypeT::BF16:
             return KUDNN_B200_BF16;
+        case Element::TypeT::S32:
+            return KUDNN_B200_S32;
+        case Element::TypeT::S8:
+            return KUDNN_B200_S8;
+        case Element::TypeT::U8:
+            return KUDNN_B200_U8;
         default:
             return 100 + static_cast<int>(t);  // rejected by kudnn_b200_linear_validate as UNSUPPORTED
     }

@@ -10,7 +10,7 @@ import subprocess
 
 import numpy as np
 
-F32, F16, BF16 = 1, 2, 3
+F32, F16, BF16, S32, S8, U8 = 1, 2, 3, 4, 5, 6
 ACT_NONE, ACT_RELU, ACT_TANH, ACT_SIGMOID, ACT_GELU_TANH, ACT_SWISH, ACT_GELU_ERF = 0, 5, 9, 10, 20, 25, 27
 RES_NONE, RES_EXT, RES_IDENTICAL, RES_ELTWISE_MUL = 0, 1, 2, 3
 ACC_F32, ACC_F64 = 0, 1
@@ -64,6 +64,8 @@ def load(path=None):
     lib.ko_num_threads.restype = ctypes.c_int
     lib.ko_activation.restype = ctypes.c_float
     lib.ko_activation.argtypes = [ctypes.c_float, ctypes.c_int, ctypes.c_float]
+    lib.ko_linear_int.restype = ctypes.c_int
+    lib.ko_linear_int.argtypes = [ctypes.POINTER(Desc)] + [ctypes.c_void_p] * 4 + [ctypes.c_float] * 2
     lib.ko_activation_run.restype = ctypes.c_int
     lib.ko_activation_run.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_int, ctypes.c_float]
@@ -79,7 +81,7 @@ def load(path=None):
 
 
 def np_dtype(code):
-    return np.float32 if code == F32 else np.uint16
+    return {F32: np.float32, S32: np.int32, S8: np.int8, U8: np.uint8}.get(code, np.uint16)
 
 
 def to_storage(x_f32, code, lib=None):
@@ -113,6 +115,11 @@ def linear(desc, a, b, c=None, bias=None, res=None, out=None, alpha=1.0, beta=0.
            num_threads=0, lib=None):
     """Evaluate one Linear(+post-op) on the CPU.  Output arrays are written in place."""
     lib = lib or load()
+    if desc.c_dtype == S32:
+        rc = lib.ko_linear_int(ctypes.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(bias), alpha, beta)
+        if rc != 0:
+            raise RuntimeError("ko_linear_int failed with code %d" % rc)
+        return
     rc = lib.ko_linear(ctypes.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(bias), _ptr(res), _ptr(out),
                        alpha, beta, gamma, acc, num_threads)
     if rc != 0:

@@ -56,6 +56,9 @@
 #define KO_F32 1
 #define KO_F16 2
 #define KO_BF16 3
+#define KO_S32 4
+#define KO_S8 5
+#define KO_U8 6
 
 #define KO_ACT_NONE 0
 #define KO_ACT_RELU 5
@@ -182,11 +185,22 @@ uint16_t ko_f32_to_f16_rne(float f)
     return (uint16_t)(sign | q);
 }
 
+static inline size_t ko_elem_size(int dtype)
+{
+    return (dtype == KO_F32 || dtype == KO_S32) ? 4 : ((dtype == KO_S8 || dtype == KO_U8) ? 1 : 2);
+}
+
 static inline float ko_load(const void *p, int dtype, int64_t idx)
 {
     switch (dtype) {
         case KO_F32:
             return ((const float *)p)[idx];
+        case KO_S8: /* widened exactly, as MatrixConverter S8 -> F16 does (kudnn_gemm.cpp:337-344) */
+            return (float)((const int8_t *)p)[idx];
+        case KO_U8:
+            return (float)((const uint8_t *)p)[idx];
+        case KO_S32:
+            return (float)((const int32_t *)p)[idx];
         case KO_F16:
             return ko_f16_to_f32(((const uint16_t *)p)[idx]);
         default:
@@ -309,7 +323,7 @@ static inline ko_pair ko_finish(const ko_desc *d, float acc, float alpha, float 
         t += beta * c_old;
     }
     float c1;
-    if (ct == KO_F16 && (!have_bias || d->bias_dtype == KO_F16)) {
+    if (ct == KO_F16 && d->a_dtype == KO_F16 && d->b_dtype == KO_F16 && (!have_bias || d->bias_dtype == KO_F16)) {
         /* hgemm writes fp16, the bias is then added in __fp16 (kudnn_gemm.cpp:189-192, :111) */
         c1 = ko_round_rne(t, KO_F16);
         if (have_bias) {
@@ -317,8 +331,8 @@ static inline ko_pair ko_finish(const ko_desc *d, float acc, float alpha, float 
         }
     } else {
         /* fp32: plain add; bf16: add in fp32 then one RNE (kudnn_gemm.cpp:216-221); fp16 result with a wider
-         * bias: no exact tuple exists, the product and the bias add run in fp32 and the result is rounded once
-         * (kudnn_gemm.cpp:679-692, and the W8A16 wrapper :348-360) */
+         * bias or with 8-bit weights (W8A16): the product and the bias add run in fp32 and the result is rounded
+         * once (kudnn_gemm.cpp:679-692 and the <fp16, s8|u8, fp16, float> wrappers :336-372) */
         if (have_bias) {
             t += bias;
         }
@@ -488,8 +502,8 @@ int ko_linear(const ko_desc *d, const void *a, const void *b, void *c, const voi
                 const int64_t obias = i0 * d->bias_sb[0] + i1 * d->bias_sb[1] + i2 * d->bias_sb[2];
                 const int64_t ores = i0 * d->res_sb[0] + i1 * d->res_sb[1] + i2 * d->res_sb[2];
                 const int64_t oout = i0 * d->out_sb[0] + i1 * d->out_sb[1] + i2 * d->out_sb[2];
-                const size_t esa = (d->a_dtype == KO_F32) ? 4 : 2;
-                const size_t esb = (d->b_dtype == KO_F32) ? 4 : 2;
+                const size_t esa = ko_elem_size(d->a_dtype);
+                const size_t esb = ko_elem_size(d->b_dtype);
                 ko_pack((const char *)a + oa * (int64_t)esa, d->a_dtype, m, k, d->a_sm, d->a_sk, pa, kp);
                 ko_pack((const char *)b + ob * (int64_t)esb, d->b_dtype, n, k, d->b_sn, d->b_sk, pb, kp);
                 const int64_t mb = (m + 3) / 4, nbk = (n + 3) / 4;
@@ -541,6 +555,61 @@ int ko_linear(const ko_desc *d, const void *a, const void *b, void *c, const voi
     }
     free(pa);
     free(pb);
+    return 0;
+}
+
+/*
+ * 8-bit integer product <s8|u8, s8|u8, s32, s32> (GEMMWrapper, src/dnn/src/kudnn_gemm.cpp:259-334: cblas_gemm_*s32
+ * with zero operand offsets, the bias passed as the row / column / fixed offset of c or added afterwards by AddBias).
+ * The arithmetic of the closed BLAS is taken to be exact 32-bit sums; with alpha = 1 and beta = 0 or 1 everything
+ * stays in integers, other scalars go through fp64 and round to nearest.  2-D or batched, any strides.
+ */
+int ko_linear_int(const ko_desc *d, const void *a, const void *b, void *c, const void *bias, float alpha, float beta)
+{
+    if (d == NULL || a == NULL || b == NULL || c == NULL || d->c_dtype != KO_S32 || (d->has_bias != 0) != (bias != NULL)) {
+        return -1;
+    }
+    const int64_t nb0 = d->batch[0] > 0 ? d->batch[0] : 1, nb1 = d->batch[1] > 0 ? d->batch[1] : 1;
+    const int64_t nb2 = d->batch[2] > 0 ? d->batch[2] : 1;
+    int32_t *cc = (int32_t *)c;
+    for (int64_t i0 = 0; i0 < nb0; ++i0) {
+        for (int64_t i1 = 0; i1 < nb1; ++i1) {
+            for (int64_t i2 = 0; i2 < nb2; ++i2) {
+                const int64_t oa = i0 * d->a_sb[0] + i1 * d->a_sb[1] + i2 * d->a_sb[2];
+                const int64_t ob = i0 * d->b_sb[0] + i1 * d->b_sb[1] + i2 * d->b_sb[2];
+                const int64_t oc = i0 * d->c_sb[0] + i1 * d->c_sb[1] + i2 * d->c_sb[2];
+                const int64_t obias = i0 * d->bias_sb[0] + i1 * d->bias_sb[1] + i2 * d->bias_sb[2];
+#pragma omp parallel for collapse(2) schedule(static)
+                for (int64_t mi = 0; mi < d->m; ++mi) {
+                    for (int64_t ni = 0; ni < d->n; ++ni) {
+                        int64_t acc = 0;
+                        for (int64_t kk = 0; kk < d->k; ++kk) {
+                            const int64_t ia = oa + mi * d->a_sm + kk * d->a_sk, ib = ob + kk * d->b_sk + ni * d->b_sn;
+                            const int av = d->a_dtype == KO_S8 ? ((const int8_t *)a)[ia] : ((const uint8_t *)a)[ia];
+                            const int bv = d->b_dtype == KO_S8 ? ((const int8_t *)b)[ib] : ((const uint8_t *)b)[ib];
+                            acc += av * bv;
+                        }
+                        const int64_t ic = oc + mi * d->c_sm + ni * d->c_sn;
+                        int64_t r = acc;
+                        if (alpha != 1.0f || (beta != 0.0f && beta != 1.0f)) {
+                            double t = (double)alpha * (double)acc;
+                            if (beta != 0.0f) {
+                                t += (double)beta * cc[ic];
+                            }
+                            r = llrint(t);
+                        } else if (beta == 1.0f) {
+                            r += cc[ic];
+                        }
+                        if (d->has_bias) {
+                            r += ((const int32_t *)bias)[obias + mi * d->bias_sm + ni * d->bias_sn];
+                        }
+                        r = r > 2147483647ll ? 2147483647ll : (r < -2147483648ll ? -2147483648ll : r);
+                        cc[ic] = (int32_t)r;
+                    }
+                }
+            }
+        }
+    }
     return 0;
 }
 

@@ -347,7 +347,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the decode-GEMV, e2e and CPU legs")
     ap.add_argument("--c5n-gather", default="fused", choices=["fused", "nccl"],
                     help="column-sharded workload: every rank's kernel writes its slab of y into all ranks' copies "
-                         "(fused), or NCCL all-gather plus a re-stride copy after the kernel (nccl)")
+                         "with plain peer stores (fused) or with one multimem.st per row piece through an NVLink "
+                         "multicast mapping of y (multimem; falls back to fused where no multicast object can be made), "
+                         "or NCCL all-gather plus a re-stride copy after the kernel (nccl)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -391,17 +393,35 @@ def main():
         m_local = w["m"] if not args.m else args.m
         nb, n_local = kb.shard_range(n_total, world, rank, 256)
         scaling = "strong"
-        par = "n-sharded x%d, " % world + ("the epilogue stores each slab of y into every rank's copy over NVLink"
-                                          if args.c5n_gather == "fused" else "NCCL all-gather of y + re-stride copy")
+        par = "n-sharded x%d, " % world + {
+            "fused": "the epilogue stores each slab of y into every rank's copy over NVLink (one store per peer)",
+            "multimem": "the epilogue stores each slab of y into every rank's copy with multimem.st through NVSwitch",
+            "nccl": "NCCL all-gather of y + re-stride copy"}[args.c5n_gather]
     else:
         m_local, n_local = w["m"], n_total
         scaling, par = "weak", ("replicas x%d: each GPU runs the full batch against replicated W" % world) if world > 1 \
             else "single GPU"
     x, wt, bias, res = make_inputs(w, m_local, device, seed=rank, n=n_local)
     tdt = x.dtype
-    fused_gather = wname == "c5n" and world > 1 and args.c5n_gather == "fused"
-    peer_ptrs, y_full_ptr = [], None
-    if fused_gather:
+    fused_gather = wname == "c5n" and world > 1 and args.c5n_gather in ("fused", "multimem")
+    peer_ptrs, y_full_ptr, y_sym, mc_ptr, multicast_note = [], None, None, 0, None
+    if fused_gather and args.c5n_gather == "multimem":
+        # y lives in symmetric memory: torch allocates it, exchanges the handles and, where the machine can, binds every
+        # rank's copy to one NVLink multicast object.  Plumbing only: the stores are issued by this library's kernel.
+        import torch.distributed._symmetric_memory as symm_mem
+        esize = x.element_size()
+        y_sym = symm_mem.empty((m_local, n_total), dtype=tdt, device=device)
+        sym = symm_mem.rendezvous(y_sym, dist.group.WORLD)
+        y_full_ptr = y_sym.data_ptr()
+        peer_ptrs = [int(p) for r, p in enumerate(sym.buffer_ptrs) if r != rank]
+        mc_ptr = int(sym.multicast_ptr) if sym.has_multicast_support(device.type, device.index) else 0
+        flag = torch.tensor([1 if mc_ptr else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            mc_ptr, multicast_note = 0, "no multicast object on this machine: plain peer stores"
+        y = y_full_ptr + nb * esize
+        desc = make_desc(kb, w, m_local, n=n_local, ldc=n_total)
+    elif fused_gather:
         # every rank holds the full [m, n_total] y in a buffer the others map; this rank's kernel writes columns
         # [nb, nb + n_local) of all of them
         esize = x.element_size()
@@ -420,6 +440,9 @@ def main():
     if fused_gather:
         mirrors = [p + nb * x.element_size() for p in peer_ptrs]
         lin.set_mirrors(None if w["res"] else mirrors, mirrors if w["res"] else None)
+        if mc_ptr:
+            mc = mc_ptr + nb * x.element_size()
+            lin.set_multicast(None if w["res"] else mc, mc if w["res"] else None)
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     drain_buf = torch.zeros(256 << 18, dtype=torch.float32, device=device)  # 256 MiB
 
@@ -436,6 +459,7 @@ def main():
         early["configs"] = other_configs_leg(torch, kb, device, peaks, flush)
         early["decode_gemv"] = gemv_leg(torch, kb, device, peaks, flush)
         early["eltwise"] = eltwise_leg(torch, kb, device, peaks, flush)
+        early["int8"] = int8_leg(torch, kb, device, flush)
         torch.cuda.synchronize()
         time.sleep(1.0)
 
@@ -569,9 +593,25 @@ def main():
         line["e2e"] = {"value": None, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                        "note": "not measured in this mode (--no-extras, or the column-sharded workload whose output "
                                "lives in peer-mapped device buffers)"}
+    if y_sym is not None:
+        # every rank must hold the same bytes: checksums of each rank's slab, compared across the copies
+        torch.cuda.synchronize()
+        dist.barrier()
+        sums = torch.stack([y_sym[:, kb.shard_range(n_total, world, r, 256)[0]:][:, :kb.shard_range(n_total, world, r, 256)[1]]
+                            .to(torch.float64).abs().sum() for r in range(world)])
+        all_sums = [torch.empty_like(sums) for _ in range(world)]
+        dist.all_gather(all_sums, sums)
+        same = all(bool(torch.equal(all_sums[0], t)) for t in all_sums) and bool((sums > 0).all())
+        line["details"]["multicast"] = {"used": bool(mc_ptr), "note": multicast_note, "copies_identical": same}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
+        # no rank frees its buffers or leaves while another may still store into them
+        torch.cuda.synchronize()
+        dist.barrier()
+        if y_sym is not None:
+            lin.set_multicast(None, None)
+            lin.set_mirrors(None, None)
         dist.barrier()
         dist.destroy_process_group()
     return 0
@@ -695,6 +735,25 @@ def eltwise_leg(torch, kb, device, peaks, flush):
     out["rmsnorm_f16_8192x4096"] = {"us": ms[len(ms) // 2] * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                                     "algorithmic_bytes": (2 * rows * axis + axis) * 2}
     return out
+
+
+def int8_leg(torch, kb, device, flush):
+    """s8 x s8 -> s32 (exact sums) on configuration 2's shape through tcgen05 kind::i8: TOP/s.  No measured integer peak
+    exists for this pool, so no fraction is given (nominal dense 8-bit rate of the part: 4500 TOP/s)."""
+    m, n, k = 4096, 11008, 4096
+    g = torch.Generator(device=device).manual_seed(0)
+    a = torch.randint(-128, 128, (m, k), generator=g, device=device, dtype=torch.int8)
+    w = torch.randint(-128, 128, (n, k), generator=g, device=device, dtype=torch.int8)
+    c = torch.empty(m, n, device=device, dtype=torch.int32)
+    stream = torch.cuda.current_stream().cuda_stream
+    lin = kb.Linear(kb.make_desc(m, n, k, kb.S8, b_dtype=kb.S8, c_dtype=kb.S32, b_strides=(1, k)))
+    lin.prepack(w, stream=stream)
+    ms = timed_steps(torch, lambda: lin.run(a, w, c, stream=stream), 20, 5, flush)
+    lin.check(stream=stream)
+    ms.sort()
+    med = ms[len(ms) // 2]
+    return {"s8s8s32_4096x11008x4096": {"us": med * 1e3, "tops": 2.0 * m * n * k / (med * 1e-3) / 1e12,
+                                        "kernel": kb.KERNEL_NAMES.get(lin.last_kernel), "launches_per_call": lin.last_launches}}
 
 
 def gemv_leg(torch, kb, device, peaks, flush):

@@ -222,6 +222,16 @@ KUDNN_B200_API int kudnn_b200_linear_check(kudnn_b200_linear_t handle, void *cud
 KUDNN_B200_API int kudnn_b200_linear_set_mirrors(kudnn_b200_linear_t handle, int count, void *const *c_mirrors,
                                                  void *const *out_mirrors);
 
+/* set_multicast: on top of set_mirrors.  c_multicast / out_multicast are the addresses at which the same output
+ * tensors are mapped through an NVLink multicast object that spans every rank's copy, this rank's included (created
+ * by the host program: cuMulticastCreate / cuMulticastBindMem / cuMemMap, or a library that does so, e.g. PyTorch's
+ * symmetric memory).  The tensor-core kernel then writes each finished 128-byte row piece with ONE multimem.st
+ * instead of a local store plus one store per mirror: the switch replicates it, so a rank sends its slab over NVLink
+ * once whatever the number of ranks.  Launches or rows that do not take that path (other kernels, unaligned rows) use
+ * the plain mirror stores, so the mirrors must stay set.  Null pointers switch it off.  A process must not exit, and
+ * its buffer must not be freed, while another rank may still store through the mapping. */
+KUDNN_B200_API int kudnn_b200_linear_set_multicast(kudnn_b200_linear_t handle, void *c_multicast, void *out_multicast);
+
 /* A device buffer other processes of this machine can map, and its 64-byte handle; open / close on the other side. */
 #define KUDNN_B200_PEER_HANDLE_BYTES 64
 KUDNN_B200_API int kudnn_b200_peer_buffer_create(size_t bytes, void **dev_ptr, unsigned char *handle_out);

@@ -66,6 +66,7 @@ EXPORTS = [
     "kudnn_b200_peer_buffer_open", "kudnn_b200_peer_buffer_close", "kudnn_b200_peer_buffer_destroy",
     "kudnn_b200_linear_unpack", "kudnn_b200_debug_set_wait", "kudnn_b200_debug_fail_allocation",
     "kudnn_b200_linear_run_sharded", "kudnn_b200_activation_validate", "kudnn_b200_activation_run", "kudnn_b200_rmsnorm_validate", "kudnn_b200_rmsnorm_run",
+    "kudnn_b200_linear_set_multicast",
 ]
 
 _lib = None
@@ -97,6 +98,7 @@ def library():
     lib.kudnn_b200_linear_run_any.argtypes = [vp, ctypes.POINTER(LinearArgs), vp]
     lib.kudnn_b200_linear_run_static_scratch.argtypes = [ctypes.POINTER(LinearDesc), ctypes.POINTER(LinearArgs), vp]
     lib.kudnn_b200_linear_set_mirrors.argtypes = [vp, i32, ctypes.POINTER(vp), ctypes.POINTER(vp)]
+    lib.kudnn_b200_linear_set_multicast.argtypes = [vp, vp, vp]
     lib.kudnn_b200_peer_buffer_create.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp), ctypes.c_char_p]
     lib.kudnn_b200_peer_buffer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
     lib.kudnn_b200_peer_buffer_close.argtypes = [vp]
@@ -316,6 +318,11 @@ class Linear:
         ca = arr_t(*(cm + [None] * (count - len(cm))))
         oa = arr_t(*(om + [None] * (count - len(om))))
         _check(self._lib.kudnn_b200_linear_set_mirrors(self._h, count, ca, oa))
+
+    def set_multicast(self, c_multicast=None, out_multicast=None):
+        """Addresses of c / out in a multicast mapping over every rank's copy (with the mirrors still set): the
+        tensor-core kernel then writes each row piece with one multimem.st.  None switches it off."""
+        _check(self._lib.kudnn_b200_linear_set_multicast(self._h, _ptr(c_multicast), _ptr(out_multicast)))
 
     @property
     def last_kernel(self):

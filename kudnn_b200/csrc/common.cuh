@@ -48,6 +48,11 @@ struct EpiParams {
     // by the same stores.  Byte distance of each mirror from c / out.
     int n_mirrors;
     long long c_delta[kMaxMirrors], out_delta[kMaxMirrors];
+    // Multicast: byte distance from c / out to the address at which the same tensor is mapped through an NVLink
+    // multicast object that spans every rank's copy (this rank's included).  Where a kernel has a multicast store
+    // path, one such store replaces the local store and all the mirror stores; elsewhere the mirrors are used.
+    int use_multicast;
+    long long c_mc_delta, out_mc_delta;
 };
 
 // Writes v (exactly representable in dtype) to base[idx] and to the same element of every mirror.

@@ -58,7 +58,8 @@ struct TcOperands {
     const void *b;  // [n, k_total] K-major
     long long lda, ldb;   // row pitch in elements
     long long k_total;    // contraction length as laid out (3*k for the split-fp32 form)
-    int kind;             // KUDNN_B200_F16 / _BF16 / _F32 (tf32 planes)
+    int kind;             // KUDNN_B200_F16 / _BF16 / _F32 (tf32 planes) / _S8 (8-bit integers, signedness below)
+    int a_signed = 1, b_signed = 1;  // kind _S8 only: whether each operand holds signed values
     // batched problems: `batch` matrices per operand, a_bstride / b_bstride elements apart (0: every entry shares one)
     long long batch = 1, a_bstride = 0, b_bstride = 0;
 };

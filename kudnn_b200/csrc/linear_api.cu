@@ -135,6 +135,7 @@ struct kudnn_b200_linear_s {
     int n_mirrors = 0;
     void *c_mirror[kb::kMaxMirrors] = {};
     void *out_mirror[kb::kMaxMirrors] = {};
+    void *c_multicast = nullptr, *out_multicast = nullptr;  // the outputs as mapped through a multicast object, or null
 
     // device-side waits: limit in SM cycles (0 = default) and the timeout test hook (kudnn_b200_debug_set_wait)
     long long wait_limit = 0;
@@ -264,6 +265,8 @@ void fill_epi(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, 
     e->m = static_cast<int>(d.m);
     e->n = static_cast<int>(d.n);
     e->n_mirrors = 0;
+    e->use_multicast = 0;
+    e->c_mc_delta = e->out_mc_delta = 0;
 }
 
 void fill_problem(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, kb::LinearProblem *p)
@@ -431,10 +434,86 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
         return rc;
     }
 
-    // ---- 8-bit integer product: exact 32-bit sums on the integer kernel
+    // ---- 8-bit integer product, exact 32-bit sums: tcgen05 kind::i8 for problems worth a tensor-core launch (2-D,
+    // alpha = 1, beta = 0), the general integer kernel for the rest
     if (d.c_dtype == KUDNN_B200_S32) {
         kb::LinearProblem ip;
         fill_problem(d, args, &ip);
+        const int forced_int = h->forced_kernel;
+        const bool packed = h->packed_key != nullptr && h->packed_key == args.b;
+        if (packed) {
+            ip.b = h->packed_raw;  // the caller's pointer (possibly host memory) is only the key
+            ip.b_sk = 1;
+            ip.b_sn = h->packed_ld;
+        }
+        const bool int_worth = static_cast<double>(d.m) * d.n * d.k >= 1.0e6 * 8 && d.k >= 32;
+        if (ip.batch_count == 1 && args.alpha == 1.0f && args.beta == 0.0f && ip.epi.n_mirrors == 0 && kb::tc_available() &&
+            (forced_int == KUDNN_B200_KERNEL_TC || (forced_int == KUDNN_B200_KERNEL_AUTO && int_worth))) {
+            kb::TcOperands ops;
+            ops.kind = KUDNN_B200_S8;
+            ops.a_signed = d.a_dtype == KUDNN_B200_S8 ? 1 : 0;
+            ops.b_signed = d.b_dtype == KUDNN_B200_S8 ? 1 : 0;
+            ops.k_total = d.k;
+            int launches = 0;
+            const long long k_pad = round_up(d.k, 16);
+            if (packed) {
+                ops.b = h->packed_ptr;
+                ops.ldb = h->packed_ld;
+            } else if (kmajor_ready(args.b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
+                ops.b = args.b;
+                ops.ldb = d.b_sn;
+            } else {
+                cudaError_t e = h->b_scratch.reserve(static_cast<size_t>(d.n) * k_pad);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "packed weights");
+                }
+                e = kb::launch_pack_kmajor(args.b, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, h->b_scratch.ptr, d.b_dtype, k_pad, k_pad, stream);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "weight pack kernel");
+                }
+                launches += 1;
+                ops.b = h->b_scratch.ptr;
+                ops.ldb = k_pad;
+            }
+            if (kmajor_ready(args.a, d.a_dtype, d.a_sm, d.a_sk, d.m)) {
+                ops.a = args.a;
+                ops.lda = d.a_sm;
+            } else {
+                cudaError_t e = h->a_scratch.reserve(static_cast<size_t>(d.m) * k_pad);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "packed activations");
+                }
+                e = kb::launch_pack_kmajor(args.a, d.a_dtype, d.m, d.k, d.a_sm, d.a_sk, h->a_scratch.ptr, d.a_dtype, k_pad, k_pad, stream);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "activation pack kernel");
+                }
+                launches += 1;
+                ops.a = h->a_scratch.ptr;
+                ops.lda = k_pad;
+            }
+            if (!(h->plan_valid && h->plan_a == ops.a && h->plan_b == ops.b && h->plan_m == d.m && !h->plan_staging)) {
+                cudaError_t e = kb::tc_make_plan(ops, d.m, d.n, h->sm_count, false, &h->tc_plan);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "tensor map encoding");
+                }
+                h->plan_a = ops.a;
+                h->plan_b = ops.b;
+                h->plan_m = d.m;
+                h->plan_staging = false;
+                h->plan_valid = true;
+            }
+            cudaError_t e = kb::launch_tc(ops, h->tc_plan, ip.epi, d.m, d.n, static_cast<kb::DeviceStatus *>(h->status.ptr), stream,
+                                          h->wait_limit, -1, nullptr);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "tensor-core kernel launch");
+            }
+            h->last_kernel = KUDNN_B200_KERNEL_TC;
+            h->last_launches = launches + 1;
+            return KUDNN_B200_OK;
+        }
+        if (forced_int == KUDNN_B200_KERNEL_TC) {
+            return fail(KUDNN_B200_UNSUPPORTED, "the tensor-core kernel takes 2-D integer products with alpha = 1 and beta = 0 only");
+        }
         if (ip.batch_count > 65535) {
             return fail(KUDNN_B200_UNSUPPORTED, "more than 65535 batch entries");
         }
@@ -495,6 +574,22 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
                             "run: every mirror needs a pointer for each output that is written, at a distance from "
                             "the primary output that is a multiple of 16 bytes");
             }
+        }
+        if (h->c_multicast != nullptr || h->out_multicast != nullptr) {
+            const long long dc = args.c != nullptr && h->c_multicast != nullptr
+                                     ? static_cast<char *>(h->c_multicast) - static_cast<char *>(args.c) : 0;
+            const long long dout = args.out != nullptr && h->out_multicast != nullptr
+                                       ? static_cast<char *>(h->out_multicast) - static_cast<char *>(args.out) : 0;
+            const bool c_ok = args.c == nullptr || (h->c_multicast != nullptr && dc % 16 == 0);
+            const bool out_ok = d.res_op == KUDNN_B200_RES_NONE || (h->out_multicast != nullptr && dout % 16 == 0);
+            if (!c_ok || !out_ok) {
+                return fail(KUDNN_B200_BAD_ARGUMENTS,
+                            "run: the multicast mapping needs a pointer for each output that is written, 16-byte congruent "
+                            "with the primary output");
+            }
+            pr.epi.use_multicast = 1;
+            pr.epi.c_mc_delta = dc;
+            pr.epi.out_mc_delta = dout;
         }
     }
     int launches = 0;
@@ -1135,7 +1230,36 @@ int kudnn_b200_linear_prepack(kudnn_b200_linear_t h, const void *b, void *cuda_s
     }
     h->plan_valid = false;
     if (d.c_dtype == KUDNN_B200_S32) {
-        return KUDNN_B200_OK;  // the integer kernel reads the weights as they are: nothing to pack
+        // 8-bit integer weights: K-major rows with a pitch of a multiple of 16 bytes, what the tensor maps of the
+        // integer tensor-core launches read; already so on the device: used in place
+        h->b_blocked.release();
+        h->blocked_kpad = 0;
+        if (on_device && kmajor_ready(b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
+            h->b_packed.release();
+            h->packed_ptr = b;
+            h->packed_raw = b;
+            h->packed_ld = d.b_sn;
+        } else {
+            const long long k_pad = round_up(d.k, 16);
+            e = h->b_packed.reserve(static_cast<size_t>(d.n) * k_pad);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "packed weights");
+            }
+            e = kb::launch_pack_kmajor(b_dev, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, h->b_packed.ptr, d.b_dtype, k_pad, k_pad, stream);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "weight pack kernel");
+            }
+            h->packed_ptr = h->b_packed.ptr;
+            h->packed_raw = h->b_packed.ptr;
+            h->packed_ld = k_pad;
+        }
+        h->packed_ktotal = d.k;
+        h->packed_key = b;
+        e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "prepack");
+        }
+        return KUDNN_B200_OK;
     }
     if (on_device && d.b_dtype != KUDNN_B200_F32 && !is_int8_dtype(d.b_dtype) && kmajor_ready(b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
         // already in the streamed layout: the packed copy is the caller's buffer itself
@@ -1532,6 +1656,17 @@ int kudnn_b200_linear_set_mirrors(kudnn_b200_linear_t h, int count, void *const 
         h->c_mirror[i] = c_mirrors != nullptr ? c_mirrors[i] : nullptr;
         h->out_mirror[i] = out_mirrors != nullptr ? out_mirrors[i] : nullptr;
     }
+    return KUDNN_B200_OK;
+}
+
+int kudnn_b200_linear_set_multicast(kudnn_b200_linear_t h, void *c_multicast, void *out_multicast)
+{
+    if (h == nullptr) {
+        return fail(KUDNN_B200_BAD_ARGUMENTS, "set_multicast: null handle");
+    }
+    std::lock_guard<std::mutex> guard(h->lock);
+    h->c_multicast = c_multicast;
+    h->out_multicast = out_multicast;
     return KUDNN_B200_OK;
 }
 

@@ -15,6 +15,10 @@ __device__ __forceinline__ void store_converted(void *dst, int dtype, long long 
         static_cast<float *>(dst)[idx] = v;
     } else if (dtype == KUDNN_B200_F16) {
         static_cast<unsigned short *>(dst)[idx] = f32_to_f16_rne_bits(v);
+    } else if (dtype == KUDNN_B200_S8) {
+        static_cast<signed char *>(dst)[idx] = static_cast<signed char>(static_cast<int>(v));  // 8-bit values are exact in fp32
+    } else if (dtype == KUDNN_B200_U8) {
+        static_cast<unsigned char *>(dst)[idx] = static_cast<unsigned char>(static_cast<int>(v));
     } else {
         static_cast<unsigned short *>(dst)[idx] = f32_to_bf16_rne_bits(v);
     }

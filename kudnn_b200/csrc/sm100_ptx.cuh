@@ -148,7 +148,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
 template <int kKind>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
-    if (kKind == KUDNN_B200_F32) {
+    if (kKind == KUDNN_B200_S8) {
+        // 8-bit integer operands (signedness of each in the instruction descriptor), 32-bit integer accumulator,
+        // 32 elements of K per instruction
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+            "}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else if (kKind == KUDNN_B200_F32) {
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
@@ -252,6 +263,19 @@ inline unsigned make_idesc(int kind, int n, int m_rows)
     d |= fmt << 10;                            // B format
     d |= static_cast<unsigned>(n >> 3) << 17;  // N / 8
     d |= static_cast<unsigned>(m_rows >> 4) << 24;  // M / 16 (256 for a CTA pair)
+    return d;
+}
+
+// Instruction descriptor of tcgen05.mma kind::i8: 32-bit integer accumulator, operands signed or unsigned 8-bit
+// integers, both K-major, dense, no saturation.
+inline unsigned make_idesc_i8(bool a_signed, bool b_signed, int n, int m_rows)
+{
+    unsigned d = 0;
+    d |= 2u << 4;                               // accumulator format: s32
+    d |= (a_signed ? 1u : 0u) << 7;             // A format: 0 = u8, 1 = s8
+    d |= (b_signed ? 1u : 0u) << 10;            // B format
+    d |= static_cast<unsigned>(n >> 3) << 17;   // N / 8
+    d |= static_cast<unsigned>(m_rows >> 4) << 24;  // M / 16
     return d;
 }
 

@@ -574,6 +574,7 @@ __device__ __noinline__ void epilogue_rows_coalesced(const EpiParams &e, uint32_
     const long long pitch = (second ? e.out_sm : e.c_sm) * dtype_size(odt);  // bytes between rows
     char *row0 = (second ? rp.out : rp.c) - static_cast<long long>(lane) * pitch;  // row of lane 0
     const long long *delta = second ? e.out_delta : e.c_delta;
+    const long long mc_delta = second ? e.out_mc_delta : e.c_mc_delta;
     const int step_bias = 8 * dtype_size(kDt > 0 ? kDt : e.bias_dtype), step_res = 8 * dtype_size(kDt > 0 ? kDt : e.res_dtype);
     const uint32_t stage_addr = smem_u32(stage);
     const uint32_t my_row = stage_addr + static_cast<uint32_t>(lane * 128);
@@ -625,9 +626,16 @@ __device__ __noinline__ void epilogue_rows_coalesced(const EpiParams &e, uint32_
                              : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                              : "r"(stage_addr + static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4))));
                 char *dst = row0 + r * pitch + col_bytes;
-                *reinterpret_cast<uint4 *>(dst) = v;
-                for (int i = 0; i < e.n_mirrors; ++i) {
-                    *reinterpret_cast<uint4 *>(dst + delta[i]) = v;
+                if (e.use_multicast != 0) {
+                    // one store through the multicast mapping: the switch writes every rank's copy, this one included
+                    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + mc_delta),
+                                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                                 : "memory");
+                } else {
+                    *reinterpret_cast<uint4 *>(dst) = v;
+                    for (int i = 0; i < e.n_mirrors; ++i) {
+                        *reinterpret_cast<uint4 *>(dst + delta[i]) = v;
+                    }
                 }
             }
         }
@@ -717,6 +725,60 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
             epilogue_group8_fast<kAct, kDt>(e, cur, rp, g * step_c, g * step_bias, g * step_res, g * step_out, g);
         } else if (row_ok) {
             epilogue_group8<kAct, (kDt < 0 ? -1 : (kDt == KUDNN_B200_F32 ? 1 : 0))>(e, cur, mi, n0 + g * 8);
+        }
+    }
+}
+
+// 8-bit integer products: the accumulator holds exact 32-bit sums; c = acc (+ bias, 32-bit integers), clamped to the
+// 32-bit range like the general kernel does.  alpha = 1 and beta = 0 (the host sends anything else elsewhere).
+__device__ __forceinline__ void epilogue_row_int(const EpiParams &e, uint32_t taddr, bool row_ok, long long mi, long long n0,
+                                                 int groups)
+{
+    if (groups <= 0) {
+        return;
+    }
+    int *crow = static_cast<int *>(e.c) + (row_ok ? mi * e.c_sm + n0 * e.c_sn : 0);
+    const int *brow = e.has_bias ? static_cast<const int *>(e.bias) + (row_ok ? mi * e.bias_sm + n0 * e.bias_sn : 0) : nullptr;
+    const bool vec = row_ok && e.c_sn == 1 && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0;
+    uint32_t next[8], cur[8];
+    tmem_load_8_issue(taddr, next);
+#pragma unroll 1
+    for (int g = 0; g < groups; ++g) {
+        __syncwarp();  // rows past m skip the stores below; the TMEM instructions need the whole warp
+        tmem_load_wait(next);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            cur[j] = next[j];
+        }
+        if (g + 1 < groups) {
+            tmem_load_8_issue(taddr + static_cast<uint32_t>((g + 1) * 8), next);
+        }
+        if (!row_ok) {
+            continue;
+        }
+        const long long left = e.n - (n0 + g * 8);
+        const int valid = left >= 8 ? 8 : static_cast<int>(left);
+        int v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            long long r = static_cast<int>(cur[j]);
+            if (brow != nullptr && j < valid) {
+                r += brow[(g * 8 + j) * e.bias_sn];
+            }
+            r = r > 2147483647ll ? 2147483647ll : (r < -2147483648ll ? -2147483648ll : r);
+            v[j] = static_cast<int>(r);
+        }
+        if (vec && valid == 8) {
+            int4 *dst = reinterpret_cast<int4 *>(crow + g * 8);
+            dst[0] = make_int4(v[0], v[1], v[2], v[3]);
+            dst[1] = make_int4(v[4], v[5], v[6], v[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < valid) {
+                    crow[(g * 8 + j) * e.c_sn] = v[j];
+                }
+            }
         }
     }
 }
@@ -868,7 +930,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     constexpr int kStageBytes = kABytes + kBBytes;
     const int kStages = p.stages;  // 3-6, what fits beside the tail (and the output staging when mirrors are written)
     constexpr int kTmemCols = 2 * kBN;
-    constexpr int kElemsPerRow = (kKind == KUDNN_B200_F32) ? 32 : 64;  // elements per 128-byte k-block row
+    constexpr int kElemsPerRow = (kKind == KUDNN_B200_F32) ? 32 : (kKind == KUDNN_B200_S8 ? 128 : 64);  // per 128-byte k-block row
 
     extern __shared__ unsigned char smem_dyn[];
     // stage buffers need 1024-byte alignment for the 128-byte swizzle pattern
@@ -1088,7 +1150,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             // A bias that is one value per column is fetched once per tile into the warp's slice of shared memory,
             // before the accumulator is awaited: the loop over column groups then has no global load on its path.
             const float *staged_bias = nullptr;
-            if (e.has_bias != 0 && e.bias_sm == 0 && e.bias_sn == 1) {
+            if (kKind != KUDNN_B200_S8 && e.has_bias != 0 && e.bias_sm == 0 && e.bias_sn == 1) {
                 __syncwarp();  // every lane is done with the previous tile's values
                 for (int i = lane; i < groups * 8; i += 32) {
                     const long long col = n0 + i;
@@ -1110,7 +1172,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                        static_cast<uint32_t>(acc * kBN);
             const uint32_t taddr_part = taddr_row + static_cast<uint32_t>(g_begin * 8);
-            if (p.splits > 1) {
+            if (kKind != KUDNN_B200_S8 && p.splits > 1) {
                 // partial tile -> this CTA's shared memory (the stage buffers: every load into them has landed and
                 // every MMA that read them has completed once the accumulator barrier has fired); it is added to
                 // the other ranks' tiles after the role branches, where all warps of the cluster meet
@@ -1125,28 +1187,32 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 }
                 break;  // one work item per CTA in this mode
             }
-            // All output-side tensors in the kernel's input type (the usual case): the epilogue variants with the
-            // element type fixed at compile time.  Any other mix, or a rarer activation: the variant that reads the
-            // types and the activation from the descriptor.
-            const bool typed = e.c_dtype == kKind && (e.has_bias == 0 || e.bias_dtype == kKind) &&
-                               (e.res_op == KUDNN_B200_RES_NONE || (e.res_dtype == kKind && e.out_dtype == kKind));
-            const int act_case = typed ? e.act : -1;
-            switch (act_case) {
-                case KUDNN_B200_ACT_NONE:
-                    epilogue_row<KUDNN_B200_ACT_NONE, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    break;
-                case KUDNN_B200_ACT_RELU:
-                    epilogue_row<KUDNN_B200_ACT_RELU, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    break;
-                case KUDNN_B200_ACT_SWISH:
-                    epilogue_row<KUDNN_B200_ACT_SWISH, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    break;
-                case KUDNN_B200_ACT_GELU_TANH:
-                    epilogue_row<KUDNN_B200_ACT_GELU_TANH, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    break;
-                default:
-                    epilogue_row<-1, -1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
-                    break;
+            if constexpr (kKind == KUDNN_B200_S8) {
+                epilogue_row_int(e, taddr_part, row_ok, mi, n0, groups);
+            } else {
+                // All output-side tensors in the kernel's input type (the usual case): the epilogue variants with the
+                // element type fixed at compile time.  Any other mix, or a rarer activation: the variant that reads the
+                // types and the activation from the descriptor.
+                const bool typed = e.c_dtype == kKind && (e.has_bias == 0 || e.bias_dtype == kKind) &&
+                                   (e.res_op == KUDNN_B200_RES_NONE || (e.res_dtype == kKind && e.out_dtype == kKind));
+                const int act_case = typed ? e.act : -1;
+                switch (act_case) {
+                    case KUDNN_B200_ACT_NONE:
+                        epilogue_row<KUDNN_B200_ACT_NONE, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
+                        break;
+                    case KUDNN_B200_ACT_RELU:
+                        epilogue_row<KUDNN_B200_ACT_RELU, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
+                        break;
+                    case KUDNN_B200_ACT_SWISH:
+                        epilogue_row<KUDNN_B200_ACT_SWISH, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
+                        break;
+                    case KUDNN_B200_ACT_GELU_TANH:
+                        epilogue_row<KUDNN_B200_ACT_GELU_TANH, kKind>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
+                        break;
+                    default:
+                        epilogue_row<-1, -1>(e, taddr_part, row_ok, mi, n0, groups, staged_bias, warp_stage, lane);
+                        break;
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -1164,51 +1230,53 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
     }
 
-    if (p.splits > 1) {
-        // ------------------------------------------------------------------ split-K: add the cluster's partial tiles
-        __syncwarp();
-        cluster_sync_all();  // all partial tiles are in place (a hardware barrier over every thread of the cluster)
-        if (warp >= 2 && *abort_flag == 0) {
-            const int unit = static_cast<int>(blockIdx.x) / p.splits;
-            const int batch = unit / p.num_tiles;
-            const int tile = unit - batch * p.num_tiles;
-            const int per_group = p.group_m * p.tiles_n;
-            const int group = tile / per_group;
-            const int first_m = group * p.group_m;
-            const int gsize = (p.tiles_m - first_m < p.group_m) ? (p.tiles_m - first_m) : p.group_m;
-            const int in_group = tile - group * per_group;
-            const int tm = first_m + in_group % gsize;
-            const int tn = in_group / gsize;
-            const float *part = reinterpret_cast<const float *>(smem);
-            EpiParams e_batch;
-            if (p.batch > 1) {
-                e_batch = epi_for_batch(p.epi, p.bp, batch);
+    if constexpr (kKind != KUDNN_B200_S8) {  // integer launches never split K
+        if (p.splits > 1) {
+            // ------------------------------------------------------------------ split-K: add the cluster's partial tiles
+            __syncwarp();
+            cluster_sync_all();  // all partial tiles are in place (a hardware barrier over every thread of the cluster)
+            if (warp >= 2 && *abort_flag == 0) {
+                const int unit = static_cast<int>(blockIdx.x) / p.splits;
+                const int batch = unit / p.num_tiles;
+                const int tile = unit - batch * p.num_tiles;
+                const int per_group = p.group_m * p.tiles_n;
+                const int group = tile / per_group;
+                const int first_m = group * p.group_m;
+                const int gsize = (p.tiles_m - first_m < p.group_m) ? (p.tiles_m - first_m) : p.group_m;
+                const int in_group = tile - group * per_group;
+                const int tm = first_m + in_group % gsize;
+                const int tn = in_group / gsize;
+                const float *part = reinterpret_cast<const float *>(smem);
+                EpiParams e_batch;
+                if (p.batch > 1) {
+                    e_batch = epi_for_batch(p.epi, p.bp, batch);
+                }
+                const EpiParams &e = p.batch > 1 ? e_batch : p.epi;
+                const uint32_t rank = cluster_rank();
+                const int epi_tid = static_cast<int>(threadIdx.x) - 64;
+                const bool typed = e.c_dtype == kKind && (e.has_bias == 0 || e.bias_dtype == kKind) &&
+                                   (e.res_op == KUDNN_B200_RES_NONE || (e.res_dtype == kKind && e.out_dtype == kKind));
+                switch (typed ? e.act : -1) {
+                    case KUDNN_B200_ACT_NONE:
+                        finish_split_rows<KUDNN_B200_ACT_NONE, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                        break;
+                    case KUDNN_B200_ACT_RELU:
+                        finish_split_rows<KUDNN_B200_ACT_RELU, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                        break;
+                    case KUDNN_B200_ACT_SWISH:
+                        finish_split_rows<KUDNN_B200_ACT_SWISH, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                        break;
+                    case KUDNN_B200_ACT_GELU_TANH:
+                        finish_split_rows<KUDNN_B200_ACT_GELU_TANH, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                        break;
+                    default:
+                        finish_split_rows<-1, -1, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
+                        break;
+                }
             }
-            const EpiParams &e = p.batch > 1 ? e_batch : p.epi;
-            const uint32_t rank = cluster_rank();
-            const int epi_tid = static_cast<int>(threadIdx.x) - 64;
-            const bool typed = e.c_dtype == kKind && (e.has_bias == 0 || e.bias_dtype == kKind) &&
-                               (e.res_op == KUDNN_B200_RES_NONE || (e.res_dtype == kKind && e.out_dtype == kKind));
-            switch (typed ? e.act : -1) {
-                case KUDNN_B200_ACT_NONE:
-                    finish_split_rows<KUDNN_B200_ACT_NONE, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    break;
-                case KUDNN_B200_ACT_RELU:
-                    finish_split_rows<KUDNN_B200_ACT_RELU, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    break;
-                case KUDNN_B200_ACT_SWISH:
-                    finish_split_rows<KUDNN_B200_ACT_SWISH, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    break;
-                case KUDNN_B200_ACT_GELU_TANH:
-                    finish_split_rows<KUDNN_B200_ACT_GELU_TANH, kKind, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    break;
-                default:
-                    finish_split_rows<-1, -1, kBN>(e, part, p.splits, rank, tm, tn, p.m, p.n, epi_tid);
-                    break;
-            }
+            __syncwarp();
+            cluster_sync_all();  // no CTA leaves while another still reads its shared memory
         }
-        __syncwarp();
-        cluster_sync_all();  // no CTA leaves while another still reads its shared memory
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -1286,6 +1354,7 @@ cudaError_t encode_kmajor(CUtensorMap *map, const void *base, int kind, long lon
     const int es = dtype_size(kind);
     const CUtensorMapDataType dt = (kind == KUDNN_B200_F32)   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : (kind == KUDNN_B200_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : (kind == KUDNN_B200_S8)  ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                                               : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(k_total), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * es};
@@ -1406,7 +1475,8 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     // pair / single CTA: 4096 rows 1.385 / 1.396, 8192 rows 2.84 / 2.85, 16384 rows 6.10 / 5.96, 32768 rows
     // 13.3 / 12.4).
     const double flops = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(ops.k_total);
-    bool pair = bn == 256 && m > kBM && flops < 6.0e12 && ops.batch == 1;  // batched launches use single CTAs
+    // batched and 8-bit integer launches use single CTAs
+    bool pair = bn == 256 && m > kBM && flops < 6.0e12 && ops.batch == 1 && ops.kind != KUDNN_B200_S8;
     if (const char *env = std::getenv("KUDNN_B200_TC_PAIR")) {
         pair = pair && std::atoi(env) != 0;
     }
@@ -1429,7 +1499,7 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     const int elems_per_row = kStageRowBytes / dtype_size(ops.kind);
     const long long num_kb = (ops.k_total + elems_per_row - 1) / elems_per_row;
     long long splits = 1;
-    if (!pair && tiles * 2 <= sm_count && num_kb >= 8) {
+    if (!pair && tiles * 2 <= sm_count && num_kb >= 8 && ops.kind != KUDNN_B200_S8) {
         long long want = std::min<long long>(sm_count / tiles, num_kb / 4);
         if (const char *env = std::getenv("KUDNN_B200_TC_SPLITS")) {
             const long long v = std::atoll(env);
@@ -1502,7 +1572,8 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.tiles_m = static_cast<int>((m + tile_rows - 1) / tile_rows);
     p.tiles_n = static_cast<int>((n + plan.block_n - 1) / plan.block_n);
     p.num_tiles = p.tiles_m * p.tiles_n;
-    p.idesc = make_idesc(ops.kind, plan.block_n, plan.pair ? 2 * kBM : kBM);
+    p.idesc = ops.kind == KUDNN_B200_S8 ? make_idesc_i8(ops.a_signed != 0, ops.b_signed != 0, plan.block_n, kBM)
+                                        : make_idesc(ops.kind, plan.block_n, plan.pair ? 2 * kBM : kBM);
     p.status = status;
     p.splits = plan.splits;
     p.kb_per_split = plan.kb_per_split;
@@ -1530,6 +1601,13 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
             default:
                 return launch_one<KUDNN_B200_BF16, 256, true>(plan, p, stream);
         }
+    }
+    if (ops.kind == KUDNN_B200_S8) {
+        if (plan.splits != 1 || ops.batch != 1) {
+            return cudaErrorInvalidValue;
+        }
+        return plan.block_n == 256 ? launch_one<KUDNN_B200_S8, 256, false>(plan, p, stream)
+                                   : launch_one<KUDNN_B200_S8, 128, false>(plan, p, stream);
     }
     if (plan.block_n == 256) {
         switch (ops.kind) {

@@ -113,3 +113,80 @@ def test_integer_products_refuse_post_operations(cuda_device):
     assert kb.capi.validate(kb.make_desc(8, 8, 8, kb.S8, c_dtype=kb.F16)) == 1
     assert kb.capi.validate(kb.make_desc(8, 8, 8, kb.BF16, b_dtype=kb.S8)) == 1
     assert kb.capi.validate(kb.make_desc(8, 8, 8, kb.F16, b_dtype=kb.U8)) == 0
+
+
+def _int_case(rng, m, n, k, acode, bcode, b_layout, bias):
+    def draw(code, shape):
+        lo, hi = (-128, 128) if code == kb.S8 else (0, 256)
+        return rng.integers(lo, hi, shape).astype(ko.np_dtype(code))
+    a = draw(acode, (m, k))
+    w = draw(bcode, (n, k))  # logical weights W[n, k]
+    if b_layout == "BA":      # K-major, as a transposed nn.Linear weight is stored
+        b_arr, b_strides = w, (1, k)
+    else:                      # [k, n], n contiguous, as the reference's tests store them
+        b_arr, b_strides = np.ascontiguousarray(w.T), (n, 1)
+    shape = {None: None, "row": (1, n), "col": (m, 1), "scalar": (1, 1), "full": (m, n)}[bias]
+    bias_arr = None if shape is None else rng.integers(-100000, 100000, shape).astype(np.int32)
+    desc = kb.make_desc(m, n, k, acode, b_dtype=bcode, c_dtype=kb.S32, b_strides=b_strides, has_bias=shape is not None,
+                        bias_dtype=kb.S32, bias_strides=(0, 0) if shape is None else (shape[1] if shape[0] > 1 else 0,
+                                                                                     1 if shape[1] > 1 else 0))
+    # sums of at most k * 255 * 255 < 2^53: the float64 product is exact
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    if bias_arr is not None:
+        ref = ref + bias_arr.astype(np.float64)
+    return desc, a, b_arr, bias_arr, ref.astype(np.int64).astype(np.int32)
+
+
+@pytest.mark.parametrize("acode,bcode", [(kb.S8, kb.S8), (kb.S8, kb.U8), (kb.U8, kb.S8), (kb.U8, kb.U8)])
+@pytest.mark.parametrize("m,n,k,b_layout", [(260, 264, 136, "BA"),    # tails in m, n and k; operands need padding
+                                            (260, 264, 144, "AB"),    # weights transposed by the pack kernel
+                                            (128, 512, 256, "BA"),    # everything read in place
+                                            (300, 1000, 1040, "AB")])
+@pytest.mark.parametrize("bias", [None, "row", "full"])
+@pytest.mark.parametrize("prepack", [False, True])
+def test_int8_products_on_tensor_cores(cuda_device, acode, bcode, m, n, k, b_layout, bias, prepack):
+    """s8/u8 x s8/u8 -> s32 through tcgen05.mma kind::i8: bit-exact against an exact float64 product, and against the
+    C oracle on the small shapes."""
+    rng = np.random.default_rng(97)
+    desc, a, b_arr, bias_arr, want = _int_case(rng, m, n, k, acode, bcode, b_layout, bias)
+    if m * n * k < 2.0e7:
+        w_kn = b_arr.T if b_layout == "BA" else b_arr
+        odesc = kb.make_desc(m, n, k, acode, b_dtype=bcode, c_dtype=kb.S32, b_strides=(n, 1), has_bias=bias is not None,
+                             bias_dtype=kb.S32, bias_strides=(desc.bias_sm, desc.bias_sn))
+        oc = np.zeros((1, m, n), dtype=np.int32)
+        ko.linear(helpers.oracle_desc(odesc), a[None], np.ascontiguousarray(w_kn)[None], oc, bias_arr)
+        assert np.array_equal(oc[0], want)
+    stream = torch.cuda.current_stream().cuda_stream
+    d_a, d_b = torch.from_numpy(a).to(cuda_device), torch.from_numpy(b_arr).to(cuda_device)
+    d_c = torch.full((m, n), -7, dtype=torch.int32, device=cuda_device)
+    d_bias = torch.from_numpy(bias_arr).to(cuda_device) if bias_arr is not None else None
+    lin = kb.Linear(desc)
+    lin.force_kernel(kb.KERNEL_TC)
+    if prepack:
+        lin.prepack(d_b, stream=stream)
+    for _ in range(2):  # the second run reuses the plan
+        lin.run(d_a, d_b, d_c, d_bias, stream=stream)
+    lin.check(stream=stream)
+    assert lin.last_kernel == kb.KERNEL_TC
+    assert np.array_equal(d_c.cpu().numpy(), want)
+    lin.close()
+
+
+def test_int8_default_dispatch_and_host_pointers(cuda_device):
+    rng = np.random.default_rng(98)
+    desc, a, b_arr, bias_arr, want = _int_case(rng, 1024, 2048, 4096, kb.U8, kb.S8, "BA", "row")
+    lin = kb.Linear(desc)
+    lin.prepack(b_arr)
+    h_c = np.zeros((1024, 2048), dtype=np.int32)
+    lin.run_host(a, b_arr, h_c, bias_arr)
+    assert lin.last_kernel == kb.KERNEL_TC
+    assert np.array_equal(h_c, want)
+    # alpha != 1 is not a tensor-core case: the general integer kernel takes it
+    d_a, d_b = torch.from_numpy(a).to(cuda_device), torch.from_numpy(b_arr).to(cuda_device)
+    d_c = torch.zeros((1024, 2048), dtype=torch.int32, device=cuda_device)
+    lin2 = kb.Linear(desc)
+    lin2.run(d_a, d_b, d_c, torch.from_numpy(bias_arr).to(cuda_device), alpha=2.0, stream=torch.cuda.current_stream().cuda_stream)
+    lin2.check(stream=torch.cuda.current_stream().cuda_stream)
+    assert lin2.last_kernel == kb.KERNEL_SIMT
+    ref = 2 * (a.astype(np.float64) @ b_arr.astype(np.float64).T) + bias_arr
+    assert np.array_equal(d_c.cpu().numpy(), ref.astype(np.int64).astype(np.int32))

@@ -69,33 +69,50 @@ __device__ __forceinline__ void store_chunk(void *dst, long long idx, const floa
     }
 }
 
-template <int kSrc, int kDst>
+// kAct >= 0: the activation is fixed at compile time and evaluated in line; -1: read from the argument, out of line.
+// A thread has four 16-byte loads in flight before it touches the first value.
+template <int kSrc, int kDst, int kAct>
 __global__ void __launch_bounds__(kEltThreads) activation_kernel(const void *src, void *dst, long long count, int act,
                                                                  float alpha)
 {
     // same type in and out: the reference's typed kernels (bf16 store truncates, relu first saturates near-overflow
     // values to infinity); different types: fp32 in between and one rounding to nearest
     constexpr bool kSame = kSrc == kDst;
+    constexpr bool kPrecise = kSrc == KUDNN_B200_F32 || !kSame;
+    constexpr int kUnroll = 4;
     const long long chunks = count / 8;
     const long long stride = static_cast<long long>(gridDim.x) * kEltThreads;
-    for (long long c = static_cast<long long>(blockIdx.x) * kEltThreads + threadIdx.x; c < chunks; c += stride) {
-        float v[8];
-        load_chunk<kSrc>(src, c * 8, v);
+    for (long long c0 = static_cast<long long>(blockIdx.x) * kEltThreads + threadIdx.x; c0 < chunks; c0 += stride * kUnroll) {
+        float v[kUnroll][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            v[j] = activation_any(v[j], act, alpha, (kSrc == KUDNN_B200_F32 || !kSame) ? 1 : 0);
-            if (kSame && kDst == KUDNN_B200_BF16 && act == KUDNN_B200_ACT_RELU && alpha != 0.0f) {
-                v[j] = relu_bf16_overflow(v[j]);
+        for (int u = 0; u < kUnroll; ++u) {
+            const long long c = c0 + u * stride;
+            if (c < chunks) {
+                load_chunk<kSrc>(src, c * 8, v[u]);
             }
         }
-        store_chunk<kDst, kSame>(dst, c * 8, v);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const long long c = c0 + u * stride;
+            if (c < chunks) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[u][j] = kAct < 0 ? activation_any(v[u][j], act, alpha, kPrecise ? 1 : 0)
+                                       : activation<kPrecise>(v[u][j], kAct, alpha);
+                    if (kSame && kDst == KUDNN_B200_BF16 && (kAct < 0 ? act : kAct) == KUDNN_B200_ACT_RELU && alpha != 0.0f) {
+                        v[u][j] = relu_bf16_overflow(v[u][j]);
+                    }
+                }
+                store_chunk<kDst, kSame>(dst, c * 8, v[u]);
+            }
+        }
     }
     // the last count % 8 elements
     const long long tail0 = chunks * 8;
     const long long t = tail0 + static_cast<long long>(blockIdx.x) * kEltThreads + threadIdx.x;
     if (t < count) {
         float x = load_as_f32(src, kSrc, t);
-        x = activation_any(x, act, alpha, (kSrc == KUDNN_B200_F32 || !kSame) ? 1 : 0);
+        x = activation_any(x, act, alpha, kPrecise ? 1 : 0);
         if (kSame) {
             store_exact(dst, kDst, t, round_act(x, kDst, act, alpha));
         } else {
@@ -116,8 +133,8 @@ __device__ __forceinline__ float block_sum(float v, float *scratch)
     }
     __syncthreads();
     float total = 0.0f;
-#pragma unroll
-    for (int w = 0; w < kEltThreads / 32; ++w) {  // fixed order: the result does not depend on timing
+    const int warps = static_cast<int>(blockDim.x) >> 5;
+    for (int w = 0; w < warps; ++w) {  // fixed order: the result does not depend on timing
         total += scratch[w];
     }
     __syncthreads();
@@ -126,8 +143,11 @@ __device__ __forceinline__ float block_sum(float v, float *scratch)
 
 constexpr int kRmsMaxChunks = 8;  // chunks of 8 elements a thread keeps in registers: rows up to 16384 elements
 
-// One CTA per row.  kResident: the row is held in registers between the two passes (one read of x from memory).
-template <int kDtype, bool kResident>
+// One CTA per row.  kChunks > 0: the row is held in registers between the two passes (one read of x from memory),
+// kChunks chunks of 8 elements per thread; kChunks = 0: rows longer than that are read twice.  The launcher gives
+// rows of up to 8192 elements to CTAs of 128 threads, so that a thread has several 16-byte loads in flight and an SM
+// holds more bytes in flight than with one chunk per thread.
+template <int kDtype, int kChunks>
 __global__ void __launch_bounds__(kEltThreads) rmsnorm_kernel(const void *src, void *dst, const void *scale, float *variance,
                                                               long long rows, int axis, int use_stats, int use_scale,
                                                               int save_stats, float eps)
@@ -136,12 +156,13 @@ __global__ void __launch_bounds__(kEltThreads) rmsnorm_kernel(const void *src, v
     const int chunks = axis / 8;  // axis is a multiple of 8 on this path
     for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
         const long long base = row * axis;
-        float x[kRmsMaxChunks][8];
+        constexpr bool kResident = kChunks > 0;
+        float x[kResident ? kChunks : 1][8];
         float sum = 0.0f;
         if (kResident || use_stats == 0) {
 #pragma unroll
-            for (int i = 0; i < kRmsMaxChunks; ++i) {
-                const int c = threadIdx.x + i * kEltThreads;
+            for (int i = 0; i < kChunks; ++i) {
+                const int c = threadIdx.x + i * static_cast<int>(blockDim.x);
                 if (kResident) {
                     if (c < chunks) {
                         load_chunk<kDtype>(src, base + c * 8ll, x[i]);
@@ -153,7 +174,7 @@ __global__ void __launch_bounds__(kEltThreads) rmsnorm_kernel(const void *src, v
                 }
             }
             if (!kResident) {
-                for (int c = threadIdx.x; c < chunks; c += kEltThreads) {
+                for (int c = threadIdx.x; c < chunks; c += static_cast<int>(blockDim.x)) {
                     float v[8];
                     load_chunk<kDtype>(src, base + c * 8ll, v);
 #pragma unroll
@@ -191,14 +212,14 @@ __global__ void __launch_bounds__(kEltThreads) rmsnorm_kernel(const void *src, v
         };
         if (kResident) {
 #pragma unroll
-            for (int i = 0; i < kRmsMaxChunks; ++i) {
-                const int c = threadIdx.x + i * kEltThreads;
+            for (int i = 0; i < kChunks; ++i) {
+                const int c = threadIdx.x + i * static_cast<int>(blockDim.x);
                 if (c < chunks) {
                     finish(c, x[i]);
                 }
             }
         } else {
-            for (int c = threadIdx.x; c < chunks; c += kEltThreads) {
+            for (int c = threadIdx.x; c < chunks; c += static_cast<int>(blockDim.x)) {
                 float v[8];
                 load_chunk<kDtype>(src, base + c * 8ll, v);
                 finish(c, v);
@@ -238,22 +259,46 @@ __global__ void __launch_bounds__(kEltThreads) rmsnorm_scalar_kernel(const void 
     }
 }
 
+template <int kSrc, int kDst>
+cudaError_t launch_act_typed(const void *src, void *dst, long long count, int act, float alpha, int grid, cudaStream_t stream)
+{
+    // the activations of the Linear path get kernels of their own when source and result share a type (the usual
+    // stand-alone use); everything else takes the generic form
+#define KB_ACT_CASE(A)                                                                                    \
+    case A:                                                                                               \
+        activation_kernel<kSrc, kDst, A><<<grid, kEltThreads, 0, stream>>>(src, dst, count, act, alpha);  \
+        break
+    if (kSrc == kDst) {
+        switch (act) {
+            KB_ACT_CASE(KUDNN_B200_ACT_RELU);
+            KB_ACT_CASE(KUDNN_B200_ACT_SWISH);
+            KB_ACT_CASE(KUDNN_B200_ACT_GELU_TANH);
+            KB_ACT_CASE(KUDNN_B200_ACT_GELU_ERF);
+            KB_ACT_CASE(KUDNN_B200_ACT_SIGMOID);
+            KB_ACT_CASE(KUDNN_B200_ACT_TANH);
+            default:
+                activation_kernel<kSrc, kDst, -1><<<grid, kEltThreads, 0, stream>>>(src, dst, count, act, alpha);
+                break;
+        }
+    } else {
+        activation_kernel<kSrc, kDst, -1><<<grid, kEltThreads, 0, stream>>>(src, dst, count, act, alpha);
+    }
+#undef KB_ACT_CASE
+    return cudaGetLastError();
+}
+
 template <int kSrc>
 cudaError_t launch_act_dst(const void *src, void *dst, long long count, int dst_dtype, int act, float alpha, int grid,
                            cudaStream_t stream)
 {
     switch (dst_dtype) {
         case KUDNN_B200_F32:
-            activation_kernel<kSrc, KUDNN_B200_F32><<<grid, kEltThreads, 0, stream>>>(src, dst, count, act, alpha);
-            break;
+            return launch_act_typed<kSrc, KUDNN_B200_F32>(src, dst, count, act, alpha, grid, stream);
         case KUDNN_B200_F16:
-            activation_kernel<kSrc, KUDNN_B200_F16><<<grid, kEltThreads, 0, stream>>>(src, dst, count, act, alpha);
-            break;
+            return launch_act_typed<kSrc, KUDNN_B200_F16>(src, dst, count, act, alpha, grid, stream);
         default:
-            activation_kernel<kSrc, KUDNN_B200_BF16><<<grid, kEltThreads, 0, stream>>>(src, dst, count, act, alpha);
-            break;
+            return launch_act_typed<kSrc, KUDNN_B200_BF16>(src, dst, count, act, alpha, grid, stream);
     }
-    return cudaGetLastError();
 }
 
 }  // namespace
@@ -280,7 +325,8 @@ cudaError_t launch_rmsnorm(const void *src, void *dst, const void *scale, float 
                            int dtype, int use_stats, int use_scale, int save_stats, float eps, int sm_count,
                            cudaStream_t stream)
 {
-    const long long cap = static_cast<long long>(sm_count) * 8;
+    const int threads = axis <= kRmsMaxChunks * 8 * 128 ? 128 : kEltThreads;
+    const long long cap = static_cast<long long>(sm_count) * 16;
     const int grid = static_cast<int>(rows < cap ? rows : cap);
     const int ax = static_cast<int>(axis);
     const uintptr_t align = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) |
@@ -291,12 +337,21 @@ cudaError_t launch_rmsnorm(const void *src, void *dst, const void *scale, float 
         if (!vec) {                                                                                                    \
             rmsnorm_scalar_kernel<DT><<<grid, kEltThreads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats,     \
                                                                         use_scale, save_stats, eps);                   \
-        } else if (axis <= kRmsMaxChunks * 8 * kEltThreads) {                                                          \
-            rmsnorm_kernel<DT, true><<<grid, kEltThreads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats,     \
-                                                                       use_scale, save_stats, eps);                    \
+        } else if (axis <= 1 * 8 * threads) {                                                                          \
+            rmsnorm_kernel<DT, 1><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, \
+                                                                save_stats, eps);                                      \
+        } else if (axis <= 2 * 8 * threads) {                                                                          \
+            rmsnorm_kernel<DT, 2><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, \
+                                                                save_stats, eps);                                      \
+        } else if (axis <= 4 * 8 * threads) {                                                                          \
+            rmsnorm_kernel<DT, 4><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, \
+                                                                save_stats, eps);                                      \
+        } else if (axis <= kRmsMaxChunks * 8 * threads) {                                                              \
+            rmsnorm_kernel<DT, kRmsMaxChunks><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, \
+                                                                            use_scale, save_stats, eps);               \
         } else {                                                                                                       \
-            rmsnorm_kernel<DT, false><<<grid, kEltThreads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats,    \
-                                                                        use_scale, save_stats, eps);                   \
+            rmsnorm_kernel<DT, 0><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, \
+                                                                save_stats, eps);                                      \
         }                                                                                                              \
     } while (0)
     switch (dtype) {

@@ -345,7 +345,7 @@ def main():
     ap.add_argument("--n", type=int, default=0, help="override the column count (smaller cases for profiler captures)")
     ap.add_argument("--k", type=int, default=0, help="override the contraction length")
     ap.add_argument("--no-extras", action="store_true", help="skip the decode-GEMV, e2e and CPU legs")
-    ap.add_argument("--c5n-gather", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--c5n-gather", default="fused", choices=["fused", "multimem", "nccl"],
                     help="column-sharded workload: every rank's kernel writes its slab of y into all ranks' copies "
                          "with plain peer stores (fused) or with one multimem.st per row piece through an NVLink "
                          "multicast mapping of y (multimem; falls back to fused where no multicast object can be made), "
@@ -414,7 +414,7 @@ def main():
         sym = symm_mem.rendezvous(y_sym, dist.group.WORLD)
         y_full_ptr = y_sym.data_ptr()
         peer_ptrs = [int(p) for r, p in enumerate(sym.buffer_ptrs) if r != rank]
-        mc_ptr = int(sym.multicast_ptr) if sym.has_multicast_support(device.type, device.index) else 0
+        mc_ptr = int(sym.multicast_ptr or 0)  # 0 where the machine cannot make a multicast object
         flag = torch.tensor([1 if mc_ptr else 0], device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:

@@ -152,3 +152,79 @@ def test_column_sharded_layer_writes_every_copy(tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     for rank, (p, out) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, "rank %d failed:\n%s" % (rank, out[-3000:])
+
+
+_MULTICAST_WORKER = r"""
+import os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.distributed._symmetric_memory as symm_mem
+sys.path.insert(0, os.environ["KUDNN_ROOT"])
+import kudnn_b200 as kb
+from oracle import ko
+from tests import helpers
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+m, n_total, k = 384, 1024, 512
+case = dict(m=m, n=n_total, k=k, dtype="bf16", bias="row", act=kb.ACT_SWISH, x_dist="normal", w_std=0.03, seed=73)
+desc_full, arrays, c = helpers.build_case(case)
+ref_c, _ = helpers.run_oracle(desc_full, arrays, c, acc=ko.ACC_F64)
+n0, cnt = kb.shard_range(n_total, world, rank, 128)
+# every rank's full [m, n_total] y in symmetric memory: peer addresses and, where the machine has it, one multicast address
+y = symm_mem.empty((m, n_total), dtype=torch.bfloat16, device=dev)
+y.zero_()
+sym = symm_mem.rendezvous(y, dist.group.WORLD)
+mc = int(sym.multicast_ptr or 0)
+flag = torch.tensor([1 if mc else 0], device=dev)
+dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+status = "multicast"
+if int(flag.item()) == 0:
+    status = "no multicast object on this machine"
+else:
+    desc = kb.make_desc(m, cnt, k, kb.BF16, has_bias=True, act=kb.ACT_SWISH, c_strides=(n_total, 1))
+    x = helpers._to_torch(arrays["a"], dev)
+    w = helpers._to_torch(np.ascontiguousarray(arrays["b"][0, n0:n0 + cnt]), dev)
+    b = helpers._to_torch(np.ascontiguousarray(arrays["bias"].reshape(-1)[n0:n0 + cnt]), dev)
+    lin = kb.Linear(desc)
+    lin.set_mirrors([int(p) + n0 * 2 for r, p in enumerate(sym.buffer_ptrs) if r != rank])
+    lin.set_multicast(mc + n0 * 2)
+    stream = torch.cuda.current_stream().cuda_stream
+    lin.run(x, w, y.data_ptr() + n0 * 2, b, stream=stream)
+    lin.check(stream=stream)
+    assert lin.last_kernel == kb.KERNEL_TC
+    torch.cuda.synchronize()
+    dist.barrier()          # every rank's slab is complete in every copy
+    got = y.cpu().view(torch.int16).numpy().view(np.uint16).reshape(1, m, n_total)
+    helpers.compare(got, ref_c, desc_full.c_dtype)
+    torch.cuda.synchronize()
+    dist.barrier()          # no rank goes on to free anything while another may still store or read
+    lin.set_multicast(None)
+    lin.set_mirrors(None)
+    lin.close()
+print("rank %d ok: %s" % (rank, status))
+torch.cuda.synchronize()
+dist.barrier()
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.gpu
+def test_column_sharded_layer_through_a_multicast_mapping(tmp_path):
+    """Two ranks, y bound to one NVLink multicast object: each slab is written once with multimem.st and must arrive in
+    both copies.  Both ranks run to the end and leave together (no rank ends while its memory is bound and in use)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "multicast_worker.py"
+    script.write_text(_MULTICAST_WORKER)
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29534", KUDNN_ROOT=ROOT)
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for rank, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, "rank %d failed:\n%s" % (rank, out[-3000:])

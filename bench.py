@@ -151,7 +151,7 @@ class ClockSampler:
             mask |= s[2]
         reasons = [name for bit, name in self.REASONS if mask & bit]
         return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
-                "samples": len(inside), "note": note}
+                "sm_mhz_min": clocks[0] if clocks else None, "samples": len(inside), "note": note}
 
 
 # ----------------------------------------------------------------------------------------------------- inputs
@@ -679,7 +679,7 @@ def cublas_leg(torch, x, wt, peaks, flush, gpu_index, steps):
     tf = 2.0 * x.shape[0] * wt.shape[0] * x.shape[1] / (my_ms * 1e-3) / 1e12
     return {"what": "torch.matmul(x, W^T), bf16, no bias or activation (cuBLAS); comparison leg", "ms_per_step": my_ms,
             "tflops": tf, "frac_of_sustained_peak": tf / peaks["bf16_tflops_sustained"], "sm_mhz": clocks.get("sm_mhz"),
-            "reasons": clocks.get("reasons"),
+            "sm_mhz_min": clocks.get("sm_mhz_min"), "clock_samples": clocks.get("samples"), "reasons": clocks.get("reasons"),
             "ms_x_mhz": my_ms * clocks["sm_mhz"] if clocks.get("sm_mhz") else None}
 
 

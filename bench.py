@@ -56,13 +56,10 @@ NCU_TRAFFIC_BYTES = {
 
 
 def c5m_traffic_bytes(rows):
-    """DRAM bytes per launch of the tensor-core kernel on `rows` rows of the large prefill layer, from ncu captures of
-    smaller launches of the same shape, scaled by the rows (the weights are streamed once per group of rows, so the
-    traffic grows in proportion to them; the full-size launch is too large to capture).  Launches of 12800 rows or more
-    take the single-CTA shape with L2 eviction priorities: 16384 rows read 9.05 GB and wrote 0.97 GB.  Shorter ones run
-    on CTA pairs: 8192 rows read 6.47 GB and wrote 0.56 GB."""
-    if 2.0 * rows * 28672 * 8192 >= 6.0e12:
-        return 10.01e9 * rows / 16384.0
+    """DRAM bytes per launch of the tensor-core kernel on `rows` rows of the large prefill layer: ncu capture of an
+    8192-row launch (dram__bytes_read.sum 6.47 GB + dram__bytes_write.sum 0.56 GB), scaled by the rows; the weights are
+    streamed once per group of 4096 rows and rows of x are fetched again for later tile columns, so the traffic grows
+    in proportion to the rows.  The full-size launch is too large to capture."""
     return 7.03e9 * rows / 8192.0
 
 

@@ -43,8 +43,6 @@ struct EpiParams {
     // fp16 result of the <fp16, fp16, fp16, fp16> instance: rounded to fp16 before the bias is added in fp16.  Every
     // other fp16 result (wider bias, 8-bit weights) adds the bias in fp32 and rounds once.
     int half_chain;
-    // outputs are written once and not read again by this kernel: streaming (evict-first) stores where a kernel has them
-    int stream_out;
     int m, n;
     // Mirrors: further copies of the outputs (same strides), e.g. the same tensor in every peer GPU's memory, written
     // by the same stores.  Byte distance of each mirror from c / out.

@@ -73,7 +73,6 @@ struct TcPlan {
     int splits, kb_per_split;
     int pair;      // 1: clusters of two CTAs share 256 x block_n tiles (cta_group::2)
     int narrow_from;  // pair mode: tiles from this index on are processed as two pieces of half the width
-    int long_launch;  // 1: L2 eviction priorities on the operand copies and streaming stores for the outputs
     unsigned char tmap_a[128] __attribute__((aligned(64)));
     unsigned char tmap_b[128] __attribute__((aligned(64)));
 };

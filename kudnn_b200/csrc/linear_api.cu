@@ -228,7 +228,6 @@ int ensure_device(Handle *h)
 
 void fill_epi(const kudnn_b200_linear_desc &d, const kudnn_b200_linear_args &a, kb::EpiParams *e)
 {
-    e->stream_out = 0;
     e->c = a.c;
     e->bias = a.bias;
     e->res = a.res;

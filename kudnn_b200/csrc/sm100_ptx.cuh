@@ -77,39 +77,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
 }
 
-// L2 eviction priority for the lines a copy brings in: 0 = normal, 1 = evict first (streamed once), 2 = evict last
-// (re-read soon by other CTAs).
-__device__ __forceinline__ uint64_t l2_policy(int kind)
-{
-    uint64_t pol;
-    if (kind == 1) {
-        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    } else if (kind == 2) {
-        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    } else {
-        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
-    }
-    return pol;
-}
-
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *tmap, uint64_t *bar, int x, int y,
-                                            uint64_t policy)
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *tmap, uint64_t *bar, int x, int y)
 {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], "
-        "[%2], %5;" ::"r"(smem_u32(smem_dst)),
-        "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
 
 // the same with a third coordinate (batch entry); the box is one entry deep
-__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *tmap, uint64_t *bar, int x, int y, int z,
-                                            uint64_t policy)
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *tmap, uint64_t *bar, int x, int y, int z)
 {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], "
-        "[%1, {%3, %4, %5}], [%2], %6;" ::"r"(smem_u32(smem_dst)),
-        "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "l"(policy)
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
 
@@ -125,12 +108,12 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_smem_addr, uint32
 // Tile load of one CTA of a pair: the data lands in this CTA's shared memory, the bytes are counted on the leader's
 // barrier (a cluster address).  No data is shared between CTAs by this copy.
 __device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *tmap, uint32_t leader_bar_addr, int x,
-                                                 int y, uint64_t policy)
+                                                 int y)
 {
     asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], "
-        "[%1, {%3, %4}], [%2], %5;" ::"r"(smem_u32(smem_dst)),
-        "l"(tmap), "r"(leader_bar_addr), "r"(x), "r"(y), "l"(policy)
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+        "[%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(tmap), "r"(leader_bar_addr), "r"(x), "r"(y)
         : "memory");
 }
 

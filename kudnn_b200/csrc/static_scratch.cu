@@ -127,7 +127,6 @@ extern "C" int kudnn_b200_linear_run_static_scratch(const kudnn_b200_linear_desc
     pr.a_dtype = d.a_dtype;
     pr.b_dtype = d.b_dtype;
     kb::EpiParams &e = pr.epi;
-    e.stream_out = 0;
     e.c = args->c;
     e.bias = args->bias;
     e.res = args->res;

@@ -77,8 +77,6 @@ struct TcParams {
     // Test hook for the timeout path: the producer of CTA 0 leaves out the loads of this k-block of its first work
     // item (-1 = never), so the MMA thread's wait for that stage runs into wait_limit.  Nothing faults or hangs.
     int skip_kb;
-    // L2 eviction priority of the operand tiles (0 normal, 1 evict first, 2 evict last)
-    int hint_a, hint_b;
 };
 
 
@@ -345,16 +343,11 @@ __device__ __forceinline__ void load8_vec(const char *p, int dtype, float (&o)[8
 }
 
 // v holds values exactly representable in dtype
-__device__ __forceinline__ void store8_vec(char *p, int dtype, const float (&v)[8], int streaming = 0)
+__device__ __forceinline__ void store8_vec(char *p, int dtype, const float (&v)[8])
 {
     if (dtype == KUDNN_B200_F32) {
-        if (streaming != 0) {
-            __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
-            __stcs(reinterpret_cast<float4 *>(p) + 1, make_float4(v[4], v[5], v[6], v[7]));
-        } else {
-            reinterpret_cast<float4 *>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
-            reinterpret_cast<float4 *>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
-        }
+        reinterpret_cast<float4 *>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4 *>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
     } else {
         unsigned w[4];
         if (dtype == KUDNN_B200_BF16) {
@@ -369,11 +362,7 @@ __device__ __forceinline__ void store8_vec(char *p, int dtype, const float (&v)[
                 w[j] = *reinterpret_cast<const unsigned *>(&h);
             }
         }
-        if (streaming != 0) {
-            __stcs(reinterpret_cast<uint4 *>(p), make_uint4(w[0], w[1], w[2], w[3]));
-        } else {
-            *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -519,14 +508,14 @@ __device__ __forceinline__ void epilogue_group8_fast(const EpiParams &e, const u
     float v[8];
     compute_c8_fast<kAct, kDt>(e, raw, rp, byte_off_bias, g, v);
     if (rp.c != nullptr) {
-        store8_vec(rp.c + byte_off_c, kDt > 0 ? kDt : e.c_dtype, v, e.stream_out);
+        store8_vec(rp.c + byte_off_c, kDt > 0 ? kDt : e.c_dtype, v);
         for (int i = 0; i < e.n_mirrors; ++i) {
             store8_vec(rp.c + e.c_delta[i] + byte_off_c, kDt > 0 ? kDt : e.c_dtype, v);
         }
     }
     if (e.res_op != KUDNN_B200_RES_NONE) {
         compute_out8_fast<kDt>(e, rp, byte_off_res, v);
-        store8_vec(rp.out + byte_off_out, kDt > 0 ? kDt : e.out_dtype, v, e.stream_out);
+        store8_vec(rp.out + byte_off_out, kDt > 0 ? kDt : e.out_dtype, v);
         for (int i = 0; i < e.n_mirrors; ++i) {
             store8_vec(rp.out + e.out_delta[i] + byte_off_out, kDt > 0 ? kDt : e.out_dtype, v);
         }
@@ -1002,7 +991,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
-            const uint64_t pol_a = l2_policy(p.hint_a), pol_b = l2_policy(p.hint_b);
             int stage = 0;
             uint32_t phase = 0;
             bool alive = true;
@@ -1035,18 +1023,18 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                             mbar_expect_tx(full_bar + stage, 2 * kStageBytes);
                         }
                         const uint32_t leader_bar = map_to_rank(smem_u32(full_bar + stage), 0u);
-                        tma_load_2d_pair(sa, &tmap_a, leader_bar, kb * kElemsPerRow, tm * kBM, pol_a);
+                        tma_load_2d_pair(sa, &tmap_a, leader_bar, kb * kElemsPerRow, tm * kBM);
                         // this CTA's half of the piece's B rows (a narrow piece uses the first half of the box only)
                         tma_load_2d_pair(sb, &tmap_b, leader_bar, kb * kElemsPerRow,
-                                         tn * kBN + n_off + static_cast<int>(pair_rank) * (width / 2), pol_b);
+                                         tn * kBN + n_off + static_cast<int>(pair_rank) * (width / 2));
                     } else {
                         mbar_expect_tx(full_bar + stage, kStageBytes);
                         if (p.batch > 1) {
-                            tma_load_3d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM, p.a_bz != 0 ? batch : 0, pol_a);
-                            tma_load_3d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN, p.b_bz != 0 ? batch : 0, pol_b);
+                            tma_load_3d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM, p.a_bz != 0 ? batch : 0);
+                            tma_load_3d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN, p.b_bz != 0 ? batch : 0);
                         } else {
-                            tma_load_2d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM, pol_a);
-                            tma_load_2d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN, pol_b);
+                            tma_load_2d(sa, &tmap_a, full_bar + stage, kb * kElemsPerRow, tm * kBM);
+                            tma_load_2d(sb, &tmap_b, full_bar + stage, kb * kElemsPerRow, tn * kBN);
                         }
                     }
                     if (++stage == kStages) {
@@ -1502,10 +1490,6 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
         pair = pair_clusters > 0;
     }
     plan->pair = pair ? 1 : 0;
-    // a launch of many milliseconds on single-CTA 128 x 256 tiles, whose output is far larger than L2
-    // (not with mirrored outputs: their row-collecting stores are ordinary stores)
-    plan->long_launch =
-        (!pair && bn == 256 && flops >= 6.0e12 && ops.batch == 1 && ops.kind != KUDNN_B200_S8 && !with_staging) ? 1 : 0;
     plan->narrow_from = 0;
     plan->block_n = bn;
     plan->stages = ((bn == 256 && !pair) ? 4 : 6) - (with_staging ? 1 : 0);
@@ -1596,23 +1580,11 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.stages = plan.stages;
     {
         // The A rows of one raster group are re-read for every tile column and should stay in L2 next to the
-        // streaming weights: at most about 64 MB of them (16 tile rows of 256 x 8192 bf16).
+        // streaming weights: at most about 64 MB of them (16 tile rows of 256 x 8192 bf16).  Measured on the 32768-row
+        // layer, ms per call for 8 / 12 / 16 tile rows per group: 13.05 / 12.84 / 12.72; DRAM traffic is the same
+        // within 3 % (the wave's working set exceeds what L2 retains either way).
         const long long tile_bytes = static_cast<long long>(tile_rows) * ops.k_total * dtype_size(ops.kind);
         long long gm = (64ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
-        // Long launches (see tc_make_plan) mark those rows "evict last", the weight tiles "evict first" and write the
-        // outputs with streaming stores, and keep the marked rows to about 16 MB (8 tile rows of 128 x 8192 bf16): the
-        // launch is limited by the board's power, and every byte that does not come from DRAM a second time is energy
-        // for the tensor cores.  Measured with the variants interleaved on one box, 32768 x 28672 x 8192 bf16, ms per
-        // call: 13.8 against 15.3 without the hints (13.9 against 14.8 on another box); 16384 rows 6.9 against 7.4.
-        // With the hints but ordinary stores it is slower than without any (16.1).  Shorter launches (CTA pairs) show
-        // no difference beyond the noise and stay as they were.
-        p.hint_a = p.hint_b = 0;
-        if (plan.long_launch != 0) {
-            gm = (16ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
-            p.hint_a = 2;
-            p.hint_b = 1;
-            p.epi.stream_out = 1;
-        }
         gm = gm < 2 ? 2 : (gm > kMaxGroupM ? kMaxGroupM : gm);
         p.group_m = static_cast<int>(gm);
     }

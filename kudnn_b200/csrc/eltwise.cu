@@ -16,6 +16,24 @@ namespace {
 
 constexpr int kEltThreads = 256;
 
+// 8 values of a 16-bit type, as loaded in one 16-byte piece
+template <int kDtype>
+__device__ __forceinline__ void unpack_chunk16(const uint4 &q, float (&v)[8])
+{
+    const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (kDtype == KUDNN_B200_BF16) {
+            v[2 * j] = __uint_as_float(w[j] << 16);
+            v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+        }
+    }
+}
+
 template <int kDtype>
 __device__ __forceinline__ void load_chunk(const void *src, long long idx, float (&v)[8])
 {
@@ -228,6 +246,87 @@ __global__ void __launch_bounds__(kEltThreads) rmsnorm_kernel(const void *src, v
     }
 }
 
+// 16-bit rows that fit in registers: like rmsnorm_kernel<kDtype, kChunks>, same arithmetic in the same order, but the row
+// is kept as loaded (4 registers per chunk) and the next row of this CTA is already on its way from memory while the
+// current one is reduced, scaled and stored.
+template <int kDtype, int kChunks>
+__global__ void __launch_bounds__(kEltThreads) rmsnorm_rows16_kernel(const void *src, void *dst, const void *scale,
+                                                                     float *variance, long long rows, int axis, int use_stats,
+                                                                     int use_scale, int save_stats, float eps)
+{
+    __shared__ float scratch[kEltThreads / 32];
+    const int chunks = axis / 8;
+    const unsigned short *in = static_cast<const unsigned short *>(src);
+    uint4 cur[kChunks], nxt[kChunks];
+    auto load_row = [&](long long row, uint4(&r)[kChunks]) {
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+            const int c = threadIdx.x + i * static_cast<int>(blockDim.x);
+            if (c < chunks) {
+                r[i] = *reinterpret_cast<const uint4 *>(in + row * axis + c * 8ll);
+            }
+        }
+    };
+    long long row = blockIdx.x;
+    if (row < rows) {
+        load_row(row, nxt);
+    }
+    for (; row < rows; row += gridDim.x) {
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+            cur[i] = nxt[i];
+        }
+        if (row + gridDim.x < rows) {
+            load_row(row + gridDim.x, nxt);
+        }
+        const long long base = row * axis;
+        float var;
+        if (use_stats != 0) {
+            var = variance[row];
+        } else {
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kChunks; ++i) {
+                if (threadIdx.x + i * static_cast<int>(blockDim.x) < chunks) {
+                    float v[8];
+                    unpack_chunk16<kDtype>(cur[i], v);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        sum = fmaf(v[j], v[j], sum);
+                    }
+                }
+            }
+            var = block_sum(sum, scratch) / static_cast<float>(axis);
+            if (save_stats != 0 && threadIdx.x == 0) {
+                variance[row] = var;
+            }
+        }
+        const float inv = 1.0f / sqrtf(var + eps);
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+            const int c = threadIdx.x + i * static_cast<int>(blockDim.x);
+            if (c < chunks) {
+                float v[8];
+                unpack_chunk16<kDtype>(cur[i], v);
+                if (use_scale != 0) {
+                    float sc[8];
+                    load_chunk<kDtype>(scale, c * 8ll, sc);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        v[j] = v[j] * (sc[j] * inv);  // scale * 1/sqrt first, as the reference does
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        v[j] = v[j] * inv;
+                    }
+                }
+                store_chunk<kDtype, false>(dst, base + c * 8ll, v);
+            }
+        }
+    }
+}
+
 // any axis length and alignment: one element at a time (small or odd rows)
 template <int kDtype>
 __global__ void __launch_bounds__(kEltThreads) rmsnorm_scalar_kernel(const void *src, void *dst, const void *scale,
@@ -332,27 +431,26 @@ cudaError_t launch_rmsnorm(const void *src, void *dst, const void *scale, float 
     const uintptr_t align = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) |
                             reinterpret_cast<uintptr_t>(use_scale != 0 ? scale : nullptr);
     const bool vec = axis % 8 == 0 && (align & (dtype == KUDNN_B200_F32 ? 31u : 15u)) == 0;
+// rows held in registers: fp32 by the generic kernel, 16-bit types by the one that keeps the next row in flight
+#define KB_RMS_RES(DT, N) ((DT) == KUDNN_B200_F32 ? rmsnorm_kernel<DT, N> : rmsnorm_rows16_kernel<DT, N>)
 #define KB_RMS_LAUNCH(DT)                                                                                              \
     do {                                                                                                               \
+        void (*kernel)(const void *, void *, const void *, float *, long long, int, int, int, int, float) =           \
+            rmsnorm_kernel<DT, 0>;                                                                                     \
+        int block = threads;                                                                                           \
         if (!vec) {                                                                                                    \
-            rmsnorm_scalar_kernel<DT><<<grid, kEltThreads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats,     \
-                                                                        use_scale, save_stats, eps);                   \
+            kernel = rmsnorm_scalar_kernel<DT>;                                                                        \
+            block = kEltThreads;                                                                                       \
         } else if (axis <= 1 * 8 * threads) {                                                                          \
-            rmsnorm_kernel<DT, 1><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, \
-                                                                save_stats, eps);                                      \
+            kernel = KB_RMS_RES(DT, 1);                                                                                \
         } else if (axis <= 2 * 8 * threads) {                                                                          \
-            rmsnorm_kernel<DT, 2><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, \
-                                                                save_stats, eps);                                      \
+            kernel = KB_RMS_RES(DT, 2);                                                                                \
         } else if (axis <= 4 * 8 * threads) {                                                                          \
-            rmsnorm_kernel<DT, 4><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, \
-                                                                save_stats, eps);                                      \
+            kernel = KB_RMS_RES(DT, 4);                                                                                \
         } else if (axis <= kRmsMaxChunks * 8 * threads) {                                                              \
-            rmsnorm_kernel<DT, kRmsMaxChunks><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, \
-                                                                            use_scale, save_stats, eps);               \
-        } else {                                                                                                       \
-            rmsnorm_kernel<DT, 0><<<grid, threads, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, \
-                                                                save_stats, eps);                                      \
+            kernel = KB_RMS_RES(DT, kRmsMaxChunks);                                                                    \
         }                                                                                                              \
+        kernel<<<grid, block, 0, stream>>>(src, dst, scale, variance, rows, ax, use_stats, use_scale, save_stats, eps); \
     } while (0)
     switch (dtype) {
         case KUDNN_B200_F32:
@@ -366,6 +464,7 @@ cudaError_t launch_rmsnorm(const void *src, void *dst, const void *scale, float 
             break;
     }
 #undef KB_RMS_LAUNCH
+#undef KB_RMS_RES
     return cudaGetLastError();
 }
 

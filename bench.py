@@ -459,7 +459,7 @@ def main():
         early["configs"] = other_configs_leg(torch, kb, device, peaks, flush)
         early["decode_gemv"] = gemv_leg(torch, kb, device, peaks, flush)
         early["eltwise"] = eltwise_leg(torch, kb, device, peaks, flush)
-        early["int8"] = int8_leg(torch, kb, device, flush)
+        early["int8"] = int8_leg(torch, kb, device, peaks, flush)
         torch.cuda.synchronize()
         time.sleep(1.0)
 
@@ -737,7 +737,7 @@ def eltwise_leg(torch, kb, device, peaks, flush):
     return out
 
 
-def int8_leg(torch, kb, device, flush):
+def int8_leg(torch, kb, device, peaks, flush):
     """s8 x s8 -> s32 (exact sums) on configuration 2's shape through tcgen05 kind::i8: TOP/s.  No measured integer peak
     exists for this pool, so no fraction is given (nominal dense 8-bit rate of the part: 4500 TOP/s)."""
     m, n, k = 4096, 11008, 4096
@@ -752,8 +752,28 @@ def int8_leg(torch, kb, device, flush):
     lin.check(stream=stream)
     ms.sort()
     med = ms[len(ms) // 2]
-    return {"s8s8s32_4096x11008x4096": {"us": med * 1e3, "tops": 2.0 * m * n * k / (med * 1e-3) / 1e12,
-                                        "kernel": kb.KERNEL_NAMES.get(lin.last_kernel), "launches_per_call": lin.last_launches}}
+    out = {"s8s8s32_4096x11008x4096": {"us": med * 1e3, "tops": 2.0 * m * n * k / (med * 1e-3) / 1e12,
+                                       "kernel": kb.KERNEL_NAMES.get(lin.last_kernel), "launches_per_call": lin.last_launches}}
+    del a, w, c, lin
+    # decode with 8-bit weights (fp16 activations, fp16 result) on configuration 4's matrix: a single row streams the
+    # weights as they are, one byte per element; more rows read their fp16 form (the bytes counted here are the 8-bit ones)
+    n, k = 28672, 8192
+    w8 = torch.randint(-128, 128, (n, k), generator=g, device=device, dtype=torch.int8)
+    for rows in (1, 4):
+        x = torch.randn(rows, k, generator=g, device=device).to(torch.float16)
+        y = torch.empty(rows, n, device=device, dtype=torch.float16)
+        lin = kb.Linear(kb.make_desc(rows, n, k, kb.F16, b_dtype=kb.S8, b_strides=(1, k)))
+        lin.prepack(w8, stream=stream)
+        ms = timed_steps(torch, lambda: lin.run(x, w8, y, stream=stream), 30, 5, flush)
+        lin.check(stream=stream)
+        ms.sort()
+        med = ms[len(ms) // 2]
+        abytes = n * k + rows * k * 2 + rows * n * 2
+        out["w8a16_decode_m%d" % rows] = {"us": med * 1e3, "gbs": abytes / (med * 1e-3) / 1e9,
+                                           "frac_of_measured_hbm": abytes / (med * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                           "kernel": kb.KERNEL_NAMES.get(lin.last_kernel), "algorithmic_bytes": abytes}
+        del lin
+    return out
 
 
 def gemv_leg(torch, kb, device, peaks, flush):

@@ -78,6 +78,21 @@ __device__ __forceinline__ void unpack2(unsigned w, float &lo, float &hi)
     }
 }
 
+// Four 8-bit integers of a word as floats: each byte is dropped into the mantissa of 2^23 (the sum is exact), signed
+// bytes after a flip of their top bit, and the offset is subtracted again.
+template <bool kSigned>
+__device__ __forceinline__ void unpack4_i8(unsigned w, float *f)
+{
+    if (kSigned) {
+        w ^= 0x80808080u;  // byte + 128 as an unsigned byte
+    }
+    const float offset = kSigned ? 8388608.0f + 128.0f : 8388608.0f;
+    f[0] = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7650)) - offset;
+    f[1] = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7651)) - offset;
+    f[2] = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7652)) - offset;
+    f[3] = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7653)) - offset;
+}
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll
@@ -89,10 +104,14 @@ __device__ __forceinline__ float warp_sum(float v)
 
 // ------------------------------------------------------------------------------------------------ FMA kernel
 
+// kDtype KUDNN_B200_S8 / _U8: 8-bit weights streamed as they are (16 per load, half the bytes of their fp16 form) and
+// widened in registers, against fp16 activations.
 template <int kDtype, int kM, int kUnroll, int kThreads, int kMinBlocks>
 __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_fma_kernel(const GemvParams p)
 {
-    constexpr int kVec = (kDtype == KUDNN_B200_F32) ? 4 : 8;  // elements per 16-byte load
+    constexpr bool kInt8 = kDtype == KUDNN_B200_S8 || kDtype == KUDNN_B200_U8;
+    constexpr int kXDtype = kInt8 ? KUDNN_B200_F16 : kDtype;  // type of the activations
+    constexpr int kVec = (kDtype == KUDNN_B200_F32) ? 4 : (kInt8 ? 16 : 8);  // elements per 16-byte load
     constexpr int kBlockK = 32 * kVec;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float *xs = reinterpret_cast<float *>(smem_raw);  // [kM][kpad]
@@ -102,9 +121,17 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_fma_kernel(const Ge
         const int mi = i / kpad, kk = i - mi * kpad;
         float v = 0.0f;
         if (kk < p.k) {
-            v = load_as_f32(p.x, kDtype, static_cast<long long>(mi) * p.x_ld + kk);
+            v = load_as_f32(p.x, kXDtype, static_cast<long long>(mi) * p.x_ld + kk);
         }
-        xs[i] = v;
+        if (kInt8) {
+            // a lane's 16 activations of a k-block are four float4 reads; the q-th reads of the 32 lanes lie side by
+            // side (element lane * 16 + q * 4 + j of the block sits at (q * 32 + lane) * 4 + j): no bank conflicts
+            const int blk = kk / kBlockK, r = kk - blk * kBlockK;
+            const int ln = r / 16, q = (r % 16) / 4, j = r % 4;
+            xs[mi * kpad + blk * kBlockK + (q * 32 + ln) * 4 + j] = v;
+        } else {
+            xs[i] = v;
+        }
     }
     __syncthreads();
 
@@ -116,7 +143,7 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_fma_kernel(const Ge
     long long f = static_cast<long long>(warp) * p.span;
     const long long f_end = (f + p.span < p.total) ? f + p.span : p.total;
     const char *wbase = static_cast<const char *>(p.w);
-    const int esize = (kDtype == KUDNN_B200_F32) ? 4 : 2;
+    const int esize = (kDtype == KUDNN_B200_F32) ? 4 : (kInt8 ? 1 : 2);
 
     while (f < f_end) {
         const long long row = f / p.kb;
@@ -143,6 +170,25 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_fma_kernel(const Ge
             for (int u = 0; u < kUnroll; ++u) {
                 if (i + u < nb) {
                     const int kk = (kb0 + i + u) * kBlockK + lane * kVec;
+                    if (kInt8) {
+                        // four weights at a time, so that only four widened values are alive
+                        const unsigned words[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+                        const float4 *xb = reinterpret_cast<const float4 *>(xs + (kb0 + i + u) * kBlockK) + lane;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            float wq[4];
+                            unpack4_i8<kDtype == KUDNN_B200_S8>(words[q], wq);
+#pragma unroll
+                            for (int mi = 0; mi < kM; ++mi) {
+                                const float4 xv = xb[mi * (kpad / 4) + q * 32];
+                                acc[mi] = fmaf(wq[0], xv.x, acc[mi]);
+                                acc[mi] = fmaf(wq[1], xv.y, acc[mi]);
+                                acc[mi] = fmaf(wq[2], xv.z, acc[mi]);
+                                acc[mi] = fmaf(wq[3], xv.w, acc[mi]);
+                            }
+                        }
+                        continue;
+                    }
                     float wf[kVec];
                     if (kDtype == KUDNN_B200_F32) {
                         wf[0] = __uint_as_float(wv[u].x);
@@ -701,12 +747,12 @@ cudaError_t launch_shape(const GemvParams &p, const GemvPlan &plan, int shape, i
 {
 #define KB_SHAPE_CASE(S, T, B)                                                                       \
     case S:                                                                                          \
-        if (kFma) {                                                                                  \
+        if constexpr (kFma) {                                                                        \
             return unroll >= 8 ? launch_fma_m<kDtype, 8, T, B>(p, plan, stream)                      \
                                : launch_fma_m<kDtype, 4, T, B>(p, plan, stream);                     \
-        } else if (kDtype != KUDNN_B200_F32) {                                                       \
-            return unroll >= 8 ? launch_mma_rows<kDtype == KUDNN_B200_F32 ? KUDNN_B200_BF16 : kDtype, 8, T, B>(p, plan, stream) \
-                               : launch_mma_rows<kDtype == KUDNN_B200_F32 ? KUDNN_B200_BF16 : kDtype, 4, T, B>(p, plan, stream); \
+        } else if constexpr (kDtype == KUDNN_B200_F16 || kDtype == KUDNN_B200_BF16) {                \
+            return unroll >= 8 ? launch_mma_rows<kDtype, 8, T, B>(p, plan, stream)                   \
+                               : launch_mma_rows<kDtype, 4, T, B>(p, plan, stream);                  \
         }                                                                                            \
         return cudaErrorInvalidValue;
     switch (shape) {
@@ -727,11 +773,19 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     if (pr.batch_count != 1 || pr.m > 16 || pr.m < 1) {
         return false;
     }
-    if (pr.a_dtype != pr.b_dtype || pr.a_sk != 1 || pr.b_sk != 1) {
+    // fp16 activations against 8-bit weights: the FMA kernel streams the weights as they are (a single row)
+    const bool w8 = pr.a_dtype == KUDNN_B200_F16 && (pr.b_dtype == KUDNN_B200_S8 || pr.b_dtype == KUDNN_B200_U8);
+    if ((pr.a_dtype != pr.b_dtype && !w8) || pr.a_sk != 1 || pr.b_sk != 1) {
         return false;
     }
-    const int dt = pr.a_dtype;
-    const int vec = (dt == KUDNN_B200_F32) ? 4 : 8;
+    // (measured on a 28672 x 8192 matrix: 64 us for one row against 85 us for the fp16 form of the weights; with 2 rows
+    // the shared-memory reads of the activations take over, 87 us, 142 us with 4, and the MMA kernel on the fp16 form
+    // is as fast or faster)
+    if (w8 && (pr.m > 1 || forced_kernel == KUDNN_B200_KERNEL_GEMV_MMA)) {
+        return false;
+    }
+    const int dt = w8 ? pr.b_dtype : pr.a_dtype;
+    const int vec = (dt == KUDNN_B200_F32) ? 4 : (w8 ? 16 : 8);
     if (pr.k % vec != 0 || (pr.m > 1 && pr.a_sm % vec != 0) || (pr.n > 1 && pr.b_sn % vec != 0) || pr.k > (1 << 24) ||
         pr.n > (1 << 28)) {
         return false;
@@ -742,7 +796,7 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     const size_t max_smem = 200 * 1024;
     int kernel = forced_kernel;
     if (kernel != KUDNN_B200_KERNEL_GEMV_FMA && kernel != KUDNN_B200_KERNEL_GEMV_MMA) {
-        kernel = (dt == KUDNN_B200_F32 || pr.m <= 1) ? KUDNN_B200_KERNEL_GEMV_FMA : KUDNN_B200_KERNEL_GEMV_MMA;
+        kernel = (dt == KUDNN_B200_F32 || pr.m <= 1 || w8) ? KUDNN_B200_KERNEL_GEMV_FMA : KUDNN_B200_KERNEL_GEMV_MMA;
     }
     plan->kernel = kernel;
     int shape = -1;
@@ -908,15 +962,22 @@ cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const Gem
     p.epi = pr.epi;
     p.w_blk = plan.kernel == KUDNN_B200_KERNEL_GEMV_MMA ? static_cast<const unsigned short *>(pr.b_blocked) : nullptr;
     p.blk_kb = static_cast<int>(pr.b_blocked_kpad / 64);
-    const int dt = pr.a_dtype;
+    const bool w8 = pr.b_dtype == KUDNN_B200_S8 || pr.b_dtype == KUDNN_B200_U8;
+    const int dt = w8 ? pr.b_dtype : pr.a_dtype;
     const int unroll = 4;
     if (plan.kernel == KUDNN_B200_KERNEL_GEMV_FMA) {
-        const int vec = (dt == KUDNN_B200_F32) ? 4 : 8;
+        const int vec = (dt == KUDNN_B200_F32) ? 4 : (w8 ? 16 : 8);
         p.kb = static_cast<int>((pr.k + 32 * vec - 1) / (32 * vec));
         p.kc = 0;
         p.total = pr.n * p.kb;
         if (dt == KUDNN_B200_F32) {
             return launch_shape<KUDNN_B200_F32, true>(p, plan, plan.shape, unroll, stream);
+        }
+        if (dt == KUDNN_B200_S8) {
+            return launch_shape<KUDNN_B200_S8, true>(p, plan, plan.shape, unroll, stream);
+        }
+        if (dt == KUDNN_B200_U8) {
+            return launch_shape<KUDNN_B200_U8, true>(p, plan, plan.shape, unroll, stream);
         }
         if (dt == KUDNN_B200_F16) {
             return launch_shape<KUDNN_B200_F16, true>(p, plan, plan.shape, unroll, stream);

@@ -136,6 +136,7 @@ struct kudnn_b200_linear_s {
     void *c_mirror[kb::kMaxMirrors] = {};
     void *out_mirror[kb::kMaxMirrors] = {};
     void *c_multicast = nullptr, *out_multicast = nullptr;  // the outputs as mapped through a multicast object, or null
+    bool packed_int8 = false;  // the packed weights are the 8-bit values themselves, K-major (decode-shaped W8A16)
 
     // device-side waits: limit in SM cycles (0 = default) and the timeout test hook (kudnn_b200_debug_set_wait)
     long long wait_limit = 0;
@@ -408,6 +409,38 @@ bool collapse_batch(const kudnn_b200_linear_desc &d, kudnn_b200_linear_desc *out
     return true;
 }
 
+// Split-K scratch of the streaming kernels: partial sums and arrival counters, grown on demand.
+int reserve_gemv_scratch(Handle *h, long long partial_floats, long long counter_count, cudaStream_t stream,
+                         kb::GemvWorkspace *ws)
+{
+    cudaError_t e = h->gemv_partials.reserve(static_cast<size_t>(partial_floats) * sizeof(float));
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "streaming-kernel scratch");
+    }
+    const bool grow = h->gemv_counters.bytes < static_cast<size_t>(counter_count) * sizeof(unsigned);
+    if (grow) {
+        e = h->gemv_counters.reserve(static_cast<size_t>(counter_count) * sizeof(unsigned));
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "streaming-kernel counters");
+        }
+    }
+    // The kernels leave the counters at zero, so they are cleared only when they are new, after a run that gave
+    // up, or when the caller moved to another stream (the clear is then ordered in front of this launch).
+    if (grow || h->counters_dirty || h->counters_stream != stream) {
+        e = cudaMemsetAsync(h->gemv_counters.ptr, 0, h->gemv_counters.bytes, stream);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "streaming-kernel counters");
+        }
+        h->counters_dirty = false;
+        h->counters_stream = stream;
+    }
+    ws->partials = static_cast<float *>(h->gemv_partials.ptr);
+    ws->counters = static_cast<unsigned *>(h->gemv_counters.ptr);
+    ws->partial_floats = static_cast<long long>(h->gemv_partials.bytes / sizeof(float));
+    ws->counter_count = static_cast<long long>(h->gemv_counters.bytes / sizeof(unsigned));
+    return KUDNN_B200_OK;
+}
+
 // `d_in` is the handle's descriptor, or a copy of it restricted to a block of rows (host-pointer pipeline)
 int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_linear_args &args, cudaStream_t stream)
 {
@@ -528,15 +561,48 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
     // ---- fp16 activations with 8-bit weights: the weights are widened to fp16, K-major, once when they are pre-packed
     // or else per call, and the problem continues as fp16 x fp16 whose fp16 result is rounded once
     if (is_int8_dtype(d.b_dtype)) {
+        const bool nb1 = batch_extent(d, 0) * batch_extent(d, 1) * batch_extent(d, 2) == 1;
+        // where the 8-bit weights are read from: the K-major copy (or the caller's own buffer) that pre-packing of a
+        // decode-shaped primitive left, else the caller's pointer with its strides
+        const bool packed8 = h->packed_int8 && h->packed_key != nullptr && h->packed_key == args.b;
+        const void *w8 = packed8 ? h->packed_raw : args.b;
+        const long long w8_sn = packed8 ? h->packed_ld : d.b_sn, w8_sk = packed8 ? 1 : d.b_sk;
+        // a single row: the FMA streaming kernel reads the 8-bit weights as they are, half the bytes of their fp16 form
+        const int forced8 = h->forced_kernel;
+        if (nb1 && d.m == 1 && h->n_mirrors == 0 &&
+            (forced8 == KUDNN_B200_KERNEL_AUTO || forced8 == KUDNN_B200_KERNEL_GEMV_FMA)) {
+            kudnn_b200_linear_desc d8 = d;
+            d8.b_sn = w8_sn;
+            d8.b_sk = w8_sk;
+            kudnn_b200_linear_args a8 = args;
+            a8.b = w8;
+            kb::LinearProblem p8;
+            fill_problem(d8, a8, &p8);
+            kb::GemvPlan plan8;
+            if (kb::gemv_plan(p8, h->sm_count, forced8, &plan8)) {
+                kb::GemvWorkspace ws8;
+                rc = reserve_gemv_scratch(h, plan8.partial_floats, plan8.counter_count, stream, &ws8);
+                if (rc != KUDNN_B200_OK) {
+                    return rc;
+                }
+                cudaError_t e = kb::launch_gemv(p8, plan8, ws8, stream);
+                if (e != cudaSuccess) {
+                    return fail_cuda(e, "streaming kernel launch");
+                }
+                h->last_kernel = plan8.kernel;
+                h->last_launches = 1;
+                return KUDNN_B200_OK;
+            }
+        }
         kudnn_b200_linear_desc dq = d;
         dq.b_dtype = KUDNN_B200_F16;
         dq.reserved = 1;
         dq.b_sk = 1;
         kudnn_b200_linear_args aq = args;
-        if (h->packed_key != nullptr && h->packed_key == args.b) {
+        if (!packed8 && h->packed_key != nullptr && h->packed_key == args.b) {
             dq.b_sn = h->packed_ld;  // the packed state stands for args.b: the inner call finds it by the same key
         } else {
-            if (batch_extent(d, 0) * batch_extent(d, 1) * batch_extent(d, 2) != 1) {
+            if (!nb1) {
                 return fail(KUDNN_B200_UNSUPPORTED, "8-bit weights of batched problems are not supported");
             }
             const long long k_pad = round_up(d.k, 8);
@@ -544,8 +610,7 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
             if (e != cudaSuccess) {
                 return fail_cuda(e, "widened weights");
             }
-            e = kb::launch_pack_kmajor(args.b, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, h->q_scratch.ptr, KUDNN_B200_F16, k_pad, k_pad,
-                                       stream);
+            e = kb::launch_pack_kmajor(w8, d.b_dtype, d.n, d.k, w8_sn, w8_sk, h->q_scratch.ptr, KUDNN_B200_F16, k_pad, k_pad, stream);
             if (e != cudaSuccess) {
                 return fail_cuda(e, "weight widening kernel");
             }
@@ -608,40 +673,12 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
     }
 
     // ---- streaming kernels (m <= 16)
-    auto reserve_gemv_scratch = [&](long long partial_floats, long long counter_count, kb::GemvWorkspace *ws) -> int {
-        cudaError_t e = h->gemv_partials.reserve(static_cast<size_t>(partial_floats) * sizeof(float));
-        if (e != cudaSuccess) {
-            return fail_cuda(e, "streaming-kernel scratch");
-        }
-        const bool grow = h->gemv_counters.bytes < static_cast<size_t>(counter_count) * sizeof(unsigned);
-        if (grow) {
-            e = h->gemv_counters.reserve(static_cast<size_t>(counter_count) * sizeof(unsigned));
-            if (e != cudaSuccess) {
-                return fail_cuda(e, "streaming-kernel counters");
-            }
-        }
-        // The kernels leave the counters at zero, so they are cleared only when they are new, after a run that gave
-        // up, or when the caller moved to another stream (the clear is then ordered in front of this launch).
-        if (grow || h->counters_dirty || h->counters_stream != stream) {
-            e = cudaMemsetAsync(h->gemv_counters.ptr, 0, h->gemv_counters.bytes, stream);
-            if (e != cudaSuccess) {
-                return fail_cuda(e, "streaming-kernel counters");
-            }
-            h->counters_dirty = false;
-            h->counters_stream = stream;
-        }
-        ws->partials = static_cast<float *>(h->gemv_partials.ptr);
-        ws->counters = static_cast<unsigned *>(h->gemv_counters.ptr);
-        ws->partial_floats = static_cast<long long>(h->gemv_partials.bytes / sizeof(float));
-        ws->counter_count = static_cast<long long>(h->gemv_counters.bytes / sizeof(unsigned));
-        return KUDNN_B200_OK;
-    };
     if (two_d && d.m <= 16 &&
         (forced == KUDNN_B200_KERNEL_AUTO || forced == KUDNN_B200_KERNEL_GEMV_FMA || forced == KUDNN_B200_KERNEL_GEMV_MMA)) {
         kb::GemvPlan plan;
         if (kb::gemv_plan(pr, h->sm_count, forced, &plan)) {
             kb::GemvWorkspace ws;
-            rc = reserve_gemv_scratch(plan.partial_floats, plan.counter_count, &ws);
+            rc = reserve_gemv_scratch(h, plan.partial_floats, plan.counter_count, stream, &ws);
             if (rc != KUDNN_B200_OK) {
                 return rc;
             }
@@ -1261,6 +1298,40 @@ int kudnn_b200_linear_prepack(kudnn_b200_linear_t h, const void *b, void *cuda_s
         }
         return KUDNN_B200_OK;
     }
+    h->packed_int8 = false;
+    if (is_int8_dtype(d.b_dtype) && d.m == 1 && d.k % 16 == 0) {
+        // fp16 activations, 8-bit weights, a single row: the streaming kernel reads the 8-bit values themselves.
+        // K-major rows with a pitch of a multiple of 16 bytes: the caller's device buffer if it is so, else a copy.
+        // Other kernels, when forced, widen from here per call.
+        h->b_blocked.release();
+        h->blocked_kpad = 0;
+        if (on_device && kmajor_ready(b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
+            h->b_packed.release();
+            h->packed_ptr = b;
+            h->packed_raw = b;
+            h->packed_ld = d.b_sn;
+        } else {
+            e = h->b_packed.reserve(static_cast<size_t>(d.n) * d.k);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "packed weights");
+            }
+            e = kb::launch_pack_kmajor(b_dev, d.b_dtype, d.n, d.k, d.b_sn, d.b_sk, h->b_packed.ptr, d.b_dtype, d.k, d.k, stream);
+            if (e != cudaSuccess) {
+                return fail_cuda(e, "weight pack kernel");
+            }
+            h->packed_ptr = h->b_packed.ptr;
+            h->packed_raw = h->b_packed.ptr;
+            h->packed_ld = d.k;
+        }
+        h->packed_ktotal = d.k;
+        h->packed_int8 = true;
+        h->packed_key = b;
+        e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "prepack");
+        }
+        return KUDNN_B200_OK;
+    }
     if (on_device && d.b_dtype != KUDNN_B200_F32 && !is_int8_dtype(d.b_dtype) && kmajor_ready(b, d.b_dtype, d.b_sn, d.b_sk, d.n)) {
         // already in the streamed layout: the packed copy is the caller's buffer itself
         h->b_packed.release();
@@ -1677,6 +1748,7 @@ int kudnn_b200_linear_unpack(kudnn_b200_linear_t h)
     }
     std::lock_guard<std::mutex> guard(h->lock);
     h->packed_key = nullptr;
+    h->packed_int8 = false;
     h->packed_ptr = nullptr;
     h->packed_raw = nullptr;
     h->packed_ld = h->packed_ktotal = 0;

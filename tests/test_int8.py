@@ -190,3 +190,25 @@ def test_int8_default_dispatch_and_host_pointers(cuda_device):
     assert lin2.last_kernel == kb.KERNEL_SIMT
     ref = 2 * (a.astype(np.float64) @ b_arr.astype(np.float64).T) + bias_arr
     assert np.array_equal(d_c.cpu().numpy(), ref.astype(np.int64).astype(np.int32))
+
+
+@pytest.mark.parametrize("wcode", [kb.S8, kb.U8])
+@pytest.mark.parametrize("m,n,k", [(1, 520, 272), (1, 1003, 1040), (1, 96, 8192), (2, 264, 528)])
+@pytest.mark.parametrize("b_layout,prepack", [("BA", False), ("BA", True), ("AB", True)])
+@pytest.mark.parametrize("bias,act,res_op", [(None, kb.ACT_NONE, kb.RES_NONE), ("f32", kb.ACT_SWISH, kb.RES_ELTWISE_MUL),
+                                              ("f16", kb.ACT_GELU_TANH, kb.RES_NONE)])
+def test_w8a16_decode_streams_the_8_bit_weights(cuda_device, wcode, m, n, k, b_layout, prepack, bias, act, res_op):
+    """One activation row and K a multiple of 16: the FMA streaming kernel reads the 8-bit weights themselves (the
+    caller's K-major buffer, or the K-major copy pre-packing makes of another layout) and widens them in registers.
+    More rows go through the fp16 form of the weights on the MMA streaming kernel."""
+    desc, arrays, c = _w8a16_case(m, n, k, wcode, bias, act, res_op, b_layout, 94)
+    ref_c, ref_o = helpers.run_oracle(desc, arrays, c, acc=ko.ACC_F64)
+    got_c, got_o, used = helpers.run_gpu(desc, arrays, c, cuda_device, prepack=prepack)   # default dispatch
+    assert used == (kb.KERNEL_GEMV_FMA if m == 1 else kb.KERNEL_GEMV_MMA)
+    helpers.compare(got_c, ref_c, desc.c_dtype)
+    if res_op != kb.RES_NONE:
+        helpers.compare(got_o, ref_o, desc.out_dtype)
+    # the same primitive on another kernel (widened from the 8-bit state) agrees within the tolerance too
+    got2_c, _, used2 = helpers.run_gpu(desc, arrays, c, cuda_device, kernel=kb.KERNEL_SIMT, prepack=prepack)
+    assert used2 == kb.KERNEL_SIMT
+    helpers.compare(got2_c, ref_c, desc.c_dtype)

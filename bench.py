@@ -345,6 +345,9 @@ def main():
     ap.add_argument("--n", type=int, default=0, help="override the column count (smaller cases for profiler captures)")
     ap.add_argument("--k", type=int, default=0, help="override the contraction length")
     ap.add_argument("--no-extras", action="store_true", help="skip the decode-GEMV, e2e and CPU legs")
+    ap.add_argument("--leg", default="", choices=["", "configs", "decode", "eltwise", "int8"],
+                    help="run only this side leg of the single-GPU line and print its object (small commands for "
+                         "profiler captures)")
     ap.add_argument("--c5n-gather", default="fused", choices=["fused", "multimem", "nccl"],
                     help="column-sharded workload: every rank's kernel writes its slab of y into all ranks' copies "
                          "with plain peer stores (fused) or with one multimem.st per row piece through an NVLink "
@@ -383,6 +386,21 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     peaks, peak_kind = load_peaks()
+
+    if args.leg:
+        fbuf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        dbuf = torch.zeros(256 << 18, dtype=torch.float32, device=device)
+
+        def leg_flush():
+            fbuf.zero_()
+            dbuf.sum()
+        leg = {"configs": lambda: other_configs_leg(torch, kb, device, peaks, leg_flush),
+               "decode": lambda: gemv_leg(torch, kb, device, peaks, leg_flush),
+               "eltwise": lambda: eltwise_leg(torch, kb, device, peaks, leg_flush),
+               "int8": lambda: int8_leg(torch, kb, device, peaks, leg_flush)}[args.leg]()
+        if rank == 0:
+            print(json.dumps({args.leg: leg}), flush=True)
+        return 0
 
     # ---- per-rank problem
     n_total = w["n"]

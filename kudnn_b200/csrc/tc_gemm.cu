@@ -1475,8 +1475,8 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
     // pair / single CTA: 4096 rows 1.385 / 1.396, 8192 rows 2.84 / 2.85, 16384 rows 6.10 / 5.96, 32768 rows
     // 13.3 / 12.4).
     const double flops = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(ops.k_total);
-    // batched and 8-bit integer launches use single CTAs
-    bool pair = bn == 256 && m > kBM && flops < 6.0e12 && ops.batch == 1 && ops.kind != KUDNN_B200_S8;
+    // batched launches use single CTAs
+    bool pair = bn == 256 && m > kBM && flops < 6.0e12 && ops.batch == 1;
     if (const char *env = std::getenv("KUDNN_B200_TC_PAIR")) {
         pair = pair && std::atoi(env) != 0;
     }
@@ -1486,6 +1486,7 @@ cudaError_t tc_make_plan(const TcOperands &ops, long long m, long long n, int sm
                             (with_staging ? kStagingBytes : 0);
         pair_clusters = ops.kind == KUDNN_B200_F32   ? max_pair_clusters<KUDNN_B200_F32>(smem)
                         : ops.kind == KUDNN_B200_F16 ? max_pair_clusters<KUDNN_B200_F16>(smem)
+                        : ops.kind == KUDNN_B200_S8  ? max_pair_clusters<KUDNN_B200_S8>(smem)
                                                      : max_pair_clusters<KUDNN_B200_BF16>(smem);
         pair = pair_clusters > 0;
     }
@@ -1572,8 +1573,9 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.tiles_m = static_cast<int>((m + tile_rows - 1) / tile_rows);
     p.tiles_n = static_cast<int>((n + plan.block_n - 1) / plan.block_n);
     p.num_tiles = p.tiles_m * p.tiles_n;
-    p.idesc = ops.kind == KUDNN_B200_S8 ? make_idesc_i8(ops.a_signed != 0, ops.b_signed != 0, plan.block_n, kBM)
-                                        : make_idesc(ops.kind, plan.block_n, plan.pair ? 2 * kBM : kBM);
+    p.idesc = ops.kind == KUDNN_B200_S8
+                  ? make_idesc_i8(ops.a_signed != 0, ops.b_signed != 0, plan.block_n, plan.pair ? 2 * kBM : kBM)
+                  : make_idesc(ops.kind, plan.block_n, plan.pair ? 2 * kBM : kBM);
     p.status = status;
     p.splits = plan.splits;
     p.kb_per_split = plan.kb_per_split;
@@ -1591,9 +1593,13 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.num_items = plan.pair ? plan.narrow_from + 2 * (p.num_tiles - plan.narrow_from)
                             : p.num_tiles * plan.splits * static_cast<int>(ops.batch);
     p.narrow_from = plan.pair ? plan.narrow_from : p.num_tiles;
-    p.idesc_narrow = make_idesc(ops.kind, plan.block_n / 2, plan.pair ? 2 * kBM : kBM);
+    p.idesc_narrow = ops.kind == KUDNN_B200_S8
+                         ? make_idesc_i8(ops.a_signed != 0, ops.b_signed != 0, plan.block_n / 2, plan.pair ? 2 * kBM : kBM)
+                         : make_idesc(ops.kind, plan.block_n / 2, plan.pair ? 2 * kBM : kBM);
     if (plan.pair) {
         switch (ops.kind) {
+            case KUDNN_B200_S8:
+                return launch_one<KUDNN_B200_S8, 256, true>(plan, p, stream);
             case KUDNN_B200_F32:
                 return launch_one<KUDNN_B200_F32, 256, true>(plan, p, stream);
             case KUDNN_B200_F16:

@@ -141,7 +141,8 @@ def _int_case(rng, m, n, k, acode, bcode, b_layout, bias):
 @pytest.mark.parametrize("m,n,k,b_layout", [(260, 264, 136, "BA"),    # tails in m, n and k; operands need padding
                                             (260, 264, 144, "AB"),    # weights transposed by the pack kernel
                                             (128, 512, 256, "BA"),    # everything read in place
-                                            (300, 1000, 1040, "AB")])
+                                            (300, 1000, 1040, "AB"),
+                                            (2560, 4096, 272, "BA")])  # CTA pairs, last wave in half-width pieces
 @pytest.mark.parametrize("bias", [None, "row", "full"])
 @pytest.mark.parametrize("prepack", [False, True])
 def test_int8_products_on_tensor_cores(cuda_device, acode, bcode, m, n, k, b_layout, bias, prepack):

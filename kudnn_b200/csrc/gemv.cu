@@ -52,6 +52,7 @@ struct GemvParams {
     // serves a few percent faster.  The MMA kernels read this copy; the FMA kernel reads the plain K-major rows.
     const unsigned short *w_blk;
     int blk_kb;  // 64-k blocks per group
+    int w8;      // MMA kernel: the weights are 8-bit integers (1 = signed, 2 = unsigned), the activations fp16
     EpiParams epi;
 };
 
@@ -91,6 +92,23 @@ __device__ __forceinline__ void unpack4_i8(unsigned w, float *f)
     f[1] = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7651)) - offset;
     f[2] = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7652)) - offset;
     f[3] = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7653)) - offset;
+}
+
+// Two pairs of 8-bit integers of a word as two half2 words (k order kept): each byte is dropped into the mantissa of
+// 1024 (exact), signed bytes after a flip of their top bit, and the offset is subtracted again in fp16 (exact).
+template <bool kSigned>
+__device__ __forceinline__ void unpack4_i8_h2(unsigned w, unsigned &lo, unsigned &hi)
+{
+    if (kSigned) {
+        w ^= 0x80808080u;
+    }
+    const unsigned off = kSigned ? 0x64806480u : 0x64006400u;  // 1024 + 128, or 1024, twice
+    const unsigned a = __byte_perm(w, 0x64646464u, 0x5140);     // bytes 0 and 1
+    const unsigned b = __byte_perm(w, 0x64646464u, 0x5342);     // bytes 2 and 3
+    const __half2 ha = __hsub2(*reinterpret_cast<const __half2 *>(&a), *reinterpret_cast<const __half2 *>(&off));
+    const __half2 hb = __hsub2(*reinterpret_cast<const __half2 *>(&b), *reinterpret_cast<const __half2 *>(&off));
+    lo = *reinterpret_cast<const unsigned *>(&ha);
+    hi = *reinterpret_cast<const unsigned *>(&hb);
 }
 
 __device__ __forceinline__ float warp_sum(float v)
@@ -349,7 +367,9 @@ __device__ __forceinline__ void mma_finish_group(const GemvParams &p, float (&ac
 // kRows16: activations occupy both 8-row halves of the 16-row operand (m > 8).
 // kWide: a block is 8 rows x 64 k and a lane loads 32 consecutive bytes of its row (two 16-byte loads), feeding four
 // MMAs; a warp instruction then touches 8 rows x 128 bytes instead of 8 x 64, which HBM serves about 5 % faster.
-template <int kDtype, bool kRows16, bool kWide, int kUnroll, int kThreads, int kMinBlocks>
+// kW8 (1 signed, 2 unsigned; with kWide and fp16): the weights are 8-bit integers read as they are, 16 bytes = 16 values
+// of a row per lane and block, and widened to fp16 in registers; the activations are laid out as for kWide.
+template <int kDtype, bool kRows16, bool kWide, int kUnroll, int kThreads, int kMinBlocks, int kW8 = 0>
 __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -397,6 +417,7 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_mma_kernel(const Ge
         const long long wrow_idx = group * 8 + gid;
         const bool row_ok = wrow_idx < p.n;
         const unsigned short *wrow = wg + wrow_idx * p.w_ld + kc0 + tig * (kLaneBytes / 2);
+        const unsigned char *wrow8 = static_cast<const unsigned char *>(p.w) + wrow_idx * p.w_ld + kc0 + tig * 16;
 
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (int i = 0; i < nb; i += kUnroll) {
@@ -407,7 +428,11 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_mma_kernel(const Ge
 #pragma unroll
                 for (int h = 0; h < (kWide ? 2 : 1); ++h) {
                     wv[u][h] = make_uint4(0u, 0u, 0u, 0u);
-                    if (p.w_blk != nullptr) {
+                    if (kW8 != 0) {
+                        if (h == 0 && i + u < nb && row_ok && (kc0 + kloc + tig * 16) < p.k) {
+                            wv[u][0] = ld_stream_16(wrow8 + kloc);
+                        }
+                    } else if (p.w_blk != nullptr) {
                         const int k_abs = kc0 + kloc + tig * (kLaneBytes / 2) + h * 8;
                         if (i + u < nb && (k_abs >> 6) < p.blk_kb) {
                             const int c = (k_abs & 63) >> 3;
@@ -430,8 +455,17 @@ __global__ void __launch_bounds__(kThreads, kMinBlocks) gemv_mma_kernel(const Ge
                         if (kRows16) {
                             xb = *reinterpret_cast<const uint4 *>(xb_row + kloc * 2 + h * 16);
                         }
-                        mma_16816<kDtype>(acc, xa.x, xb.x, xa.y, xb.y, wv[u][h].x, wv[u][h].y);
-                        mma_16816<kDtype>(acc, xa.z, xb.z, xa.w, xb.w, wv[u][h].z, wv[u][h].w);
+                        if (kW8 != 0) {
+                            // values 8h .. 8h + 7 of the lane's 16: two words of the one load
+                            unsigned c0, c1, c2, c3;
+                            unpack4_i8_h2<kW8 == 1>(h == 0 ? wv[u][0].x : wv[u][0].z, c0, c1);
+                            unpack4_i8_h2<kW8 == 1>(h == 0 ? wv[u][0].y : wv[u][0].w, c2, c3);
+                            mma_16816<kDtype>(acc, xa.x, xb.x, xa.y, xb.y, c0, c1);
+                            mma_16816<kDtype>(acc, xa.z, xb.z, xa.w, xb.w, c2, c3);
+                        } else {
+                            mma_16816<kDtype>(acc, xa.x, xb.x, xa.y, xb.y, wv[u][h].x, wv[u][h].y);
+                            mma_16816<kDtype>(acc, xa.z, xb.z, xa.w, xb.w, wv[u][h].z, wv[u][h].w);
+                        }
                     }
                 }
             }
@@ -699,6 +733,26 @@ cudaError_t launch_fma_m(const GemvParams &p, const GemvPlan &plan, cudaStream_t
 template <int kDtype, int kUnroll, int kThreads, int kMinBlocks>
 cudaError_t launch_mma_rows(const GemvParams &p, const GemvPlan &plan, cudaStream_t stream)
 {
+    if (p.w8 != 0) {
+        if constexpr (kDtype == KUDNN_B200_F16) {
+#define KB_W8_CASE(ROWS16, SIGN)                                                                                   \
+    {                                                                                                              \
+        auto kernel = gemv_mma_kernel<kDtype, ROWS16, true, kUnroll, kThreads, kMinBlocks, SIGN>;                    \
+        cudaError_t e = set_smem(kernel, plan.smem_bytes);                                                         \
+        if (e != cudaSuccess) return e;                                                                            \
+        kernel<<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);                                             \
+    }
+            if (p.m > 8) {
+                if (p.w8 == 1) KB_W8_CASE(true, 1) else KB_W8_CASE(true, 2)
+            } else {
+                if (p.w8 == 1) KB_W8_CASE(false, 1) else KB_W8_CASE(false, 2)
+            }
+#undef KB_W8_CASE
+            return cudaGetLastError();
+        } else {
+            return cudaErrorInvalidValue;
+        }
+    }
     if (p.m > 8 && plan.wide != 0) {
         auto kernel = gemv_mma_kernel<kDtype, true, true, (kUnroll > 2 ? kUnroll / 2 : 1), kThreads, kMinBlocks>;
         cudaError_t e = set_smem(kernel, plan.smem_bytes);
@@ -778,10 +832,10 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     if ((pr.a_dtype != pr.b_dtype && !w8) || pr.a_sk != 1 || pr.b_sk != 1) {
         return false;
     }
-    // (measured on a 28672 x 8192 matrix: 64 us for one row against 85 us for the fp16 form of the weights; with 2 rows
-    // the shared-memory reads of the activations take over, 87 us, 142 us with 4, and the MMA kernel on the fp16 form
-    // is as fast or faster)
-    if (w8 && (pr.m > 1 || forced_kernel == KUDNN_B200_KERNEL_GEMV_MMA)) {
+    // The 8-bit weights are streamed as they are.  One row: FMA kernel (64 us on a 28672 x 8192 matrix against 85 us for
+    // the fp16 form of the weights; with 2 rows its shared-memory reads of the activations take over, 87 us, 142 us
+    // with 4).  More rows: the MMA kernel, which widens the values to fp16 in registers.
+    if (w8 && pr.m > 1 && forced_kernel == KUDNN_B200_KERNEL_GEMV_FMA) {
         return false;
     }
     const int dt = w8 ? pr.b_dtype : pr.a_dtype;
@@ -796,7 +850,7 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     const size_t max_smem = 200 * 1024;
     int kernel = forced_kernel;
     if (kernel != KUDNN_B200_KERNEL_GEMV_FMA && kernel != KUDNN_B200_KERNEL_GEMV_MMA) {
-        kernel = (dt == KUDNN_B200_F32 || pr.m <= 1 || w8) ? KUDNN_B200_KERNEL_GEMV_FMA : KUDNN_B200_KERNEL_GEMV_MMA;
+        kernel = (dt == KUDNN_B200_F32 || pr.m <= 1) ? KUDNN_B200_KERNEL_GEMV_FMA : KUDNN_B200_KERNEL_GEMV_MMA;
     }
     plan->kernel = kernel;
     int shape = -1;
@@ -848,7 +902,7 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     // which run every feed on every shape: KUDNN_B200_GEMV_STAGED forces the staged feed for every m (1) or turns it
     // off (0), KUDNN_B200_GEMV_WIDE=0 makes the fragment-shaped loads 16 bytes per lane.
     const int staged_env = env_int("KUDNN_B200_GEMV_STAGED", -1);
-    const bool staged = staged_env < 0 ? (rows == 8 && pr.b_blocked != nullptr) : staged_env != 0;
+    const bool staged = !w8 && (staged_env < 0 ? (rows == 8 && pr.b_blocked != nullptr) : staged_env != 0);
     if (staged && (shape < 0 || shape == kStagedShape)) {
         // staged feed: 512 threads, one CTA per SM, blocks of 8 rows x 256 k
         const int warps = kStagedThreads / 32;
@@ -896,7 +950,7 @@ bool gemv_plan(const LinearProblem &pr, int sm_count, int forced_kernel, GemvPla
     const size_t smem_budget = (kShapes[shape].min_blocks == 2) ? 100 * 1024 : max_smem;
     int ksplit = 0;
     // 16 activation rows: blocks of 64 k with 32 bytes per lane (see gemv_mma_kernel)
-    const bool wide = rows == 16 && env_int("KUDNN_B200_GEMV_WIDE", 1) != 0;
+    const bool wide = w8 || (rows == 16 && env_int("KUDNN_B200_GEMV_WIDE", 1) != 0);
     const long long block_k = wide ? 64 : 32;
     if (ksplit <= 0) {
         ksplit = 1;
@@ -961,6 +1015,7 @@ cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const Gem
     p.counters = ws.counters;
     p.epi = pr.epi;
     p.w_blk = plan.kernel == KUDNN_B200_KERNEL_GEMV_MMA ? static_cast<const unsigned short *>(pr.b_blocked) : nullptr;
+    p.w8 = pr.b_dtype == KUDNN_B200_S8 ? 1 : (pr.b_dtype == KUDNN_B200_U8 ? 2 : 0);
     p.blk_kb = static_cast<int>(pr.b_blocked_kpad / 64);
     const bool w8 = pr.b_dtype == KUDNN_B200_S8 || pr.b_dtype == KUDNN_B200_U8;
     const int dt = w8 ? pr.b_dtype : pr.a_dtype;
@@ -997,7 +1052,7 @@ cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const Gem
     p.kc = static_cast<int>(kc);
     p.kb = static_cast<int>(kc / block_k);
     p.total = ((pr.n + 7) / 8) * p.kb;
-    if (dt == KUDNN_B200_F16) {
+    if (pr.a_dtype == KUDNN_B200_F16) {
         return launch_shape<KUDNN_B200_F16, false>(p, plan, plan.shape, unroll, stream);
     }
     return launch_shape<KUDNN_B200_BF16, false>(p, plan, plan.shape, unroll, stream);

@@ -567,10 +567,10 @@ int run_device(Handle *h, const kudnn_b200_linear_desc &d_in, const kudnn_b200_l
         const bool packed8 = h->packed_int8 && h->packed_key != nullptr && h->packed_key == args.b;
         const void *w8 = packed8 ? h->packed_raw : args.b;
         const long long w8_sn = packed8 ? h->packed_ld : d.b_sn, w8_sk = packed8 ? 1 : d.b_sk;
-        // a single row: the FMA streaming kernel reads the 8-bit weights as they are, half the bytes of their fp16 form
+        // decode shapes: the streaming kernels read the 8-bit weights as they are, half the bytes of their fp16 form
         const int forced8 = h->forced_kernel;
-        if (nb1 && d.m == 1 && h->n_mirrors == 0 &&
-            (forced8 == KUDNN_B200_KERNEL_AUTO || forced8 == KUDNN_B200_KERNEL_GEMV_FMA)) {
+        if (nb1 && d.m <= 16 && h->n_mirrors == 0 &&
+            (forced8 == KUDNN_B200_KERNEL_AUTO || forced8 == KUDNN_B200_KERNEL_GEMV_FMA || forced8 == KUDNN_B200_KERNEL_GEMV_MMA)) {
             kudnn_b200_linear_desc d8 = d;
             d8.b_sn = w8_sn;
             d8.b_sk = w8_sk;
@@ -1299,8 +1299,8 @@ int kudnn_b200_linear_prepack(kudnn_b200_linear_t h, const void *b, void *cuda_s
         return KUDNN_B200_OK;
     }
     h->packed_int8 = false;
-    if (is_int8_dtype(d.b_dtype) && d.m == 1 && d.k % 16 == 0) {
-        // fp16 activations, 8-bit weights, a single row: the streaming kernel reads the 8-bit values themselves.
+    if (is_int8_dtype(d.b_dtype) && d.m <= 16 && d.k % 16 == 0) {
+        // fp16 activations, 8-bit weights, decode shapes: the streaming kernels read the 8-bit values themselves.
         // K-major rows with a pitch of a multiple of 16 bytes: the caller's device buffer if it is so, else a copy.
         // Other kernels, when forced, widen from here per call.
         h->b_blocked.release();

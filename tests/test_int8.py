@@ -194,14 +194,15 @@ def test_int8_default_dispatch_and_host_pointers(cuda_device):
 
 
 @pytest.mark.parametrize("wcode", [kb.S8, kb.U8])
-@pytest.mark.parametrize("m,n,k", [(1, 520, 272), (1, 1003, 1040), (1, 96, 8192), (2, 264, 528)])
+@pytest.mark.parametrize("m,n,k", [(1, 520, 272), (1, 1003, 1040), (1, 96, 8192), (2, 264, 528), (4, 1003, 1040),
+                                   (8, 96, 2064), (12, 264, 528), (16, 520, 1040)])
 @pytest.mark.parametrize("b_layout,prepack", [("BA", False), ("BA", True), ("AB", True)])
 @pytest.mark.parametrize("bias,act,res_op", [(None, kb.ACT_NONE, kb.RES_NONE), ("f32", kb.ACT_SWISH, kb.RES_ELTWISE_MUL),
                                               ("f16", kb.ACT_GELU_TANH, kb.RES_NONE)])
 def test_w8a16_decode_streams_the_8_bit_weights(cuda_device, wcode, m, n, k, b_layout, prepack, bias, act, res_op):
-    """One activation row and K a multiple of 16: the FMA streaming kernel reads the 8-bit weights themselves (the
-    caller's K-major buffer, or the K-major copy pre-packing makes of another layout) and widens them in registers.
-    More rows go through the fp16 form of the weights on the MMA streaming kernel."""
+    """Decode shapes with K a multiple of 16: the streaming kernels read the 8-bit weights themselves (the caller's
+    K-major buffer, or the K-major copy pre-packing makes of another layout) and widen them in registers: the FMA kernel
+    for one activation row, the MMA kernel for 2 to 16."""
     desc, arrays, c = _w8a16_case(m, n, k, wcode, bias, act, res_op, b_layout, 94)
     ref_c, ref_o = helpers.run_oracle(desc, arrays, c, acc=ko.ACC_F64)
     got_c, got_o, used = helpers.run_gpu(desc, arrays, c, cuda_device, prepack=prepack)   # default dispatch

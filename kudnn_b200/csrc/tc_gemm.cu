@@ -562,6 +562,33 @@ __device__ __forceinline__ void pack8_to_chunks(const float (&v)[8], int dtype, 
     }
 }
 
+// The one 16-bit output of this thread for a group of 8 columns, packed into 16 bytes: c, or the second output when c
+// is not written.
+template <int kAct, int kDt>
+__device__ __forceinline__ uint4 epilogue_group8_packed(const EpiParams &e, const uint32_t (&raw)[8], const RowPointers &rp,
+                                                        int byte_off_bias, int byte_off_res, int g)
+{
+    float v[8];
+    compute_c8_fast<kAct, kDt>(e, raw, rp, byte_off_bias, g, v);
+    int dt = kDt > 0 ? kDt : e.c_dtype;
+    if (rp.c == nullptr) {
+        compute_out8_fast<kDt>(e, rp, byte_off_res, v);
+        dt = kDt > 0 ? kDt : e.out_dtype;
+    }
+    uint4 lo, hi;
+    pack8_to_chunks(v, dt, lo, hi);
+    return lo;
+}
+
+// 32 bytes = one whole sector of the row: L2 takes it as it is, where a 16-byte store makes it merge the bytes into the
+// sector it holds (measured: a thread's 16-byte stores cost the epilogue about 1000 cycles per column group)
+__device__ __forceinline__ void store_32(char *p, const uint4 &a, const uint4 &b)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+                 "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
 template <int kAct, int kDt>
 __device__ __noinline__ void epilogue_rows_coalesced(const EpiParams &e, uint32_t taddr, int groups, const RowPointers rp,
                                                         unsigned char *stage, int lane)
@@ -708,6 +735,14 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
     const int step_c = 8 * dtype_size(kDt > 0 ? kDt : e.c_dtype), step_bias = 8 * dtype_size(kDt > 0 ? kDt : e.bias_dtype);
     const int step_res = 8 * dtype_size(kDt > 0 ? kDt : e.res_dtype), step_out = 8 * dtype_size(kDt > 0 ? kDt : e.out_dtype);
 
+    // One 16-bit output and no mirrors: two neighbouring column groups leave as one 32-byte store wherever the first of
+    // them starts a sector (the groups of a part are consecutive, so all but a ragged first or last one pair up).
+    const int odt = rp.c != nullptr ? (kDt > 0 ? kDt : e.c_dtype) : (kDt > 0 ? kDt : e.out_dtype);
+    const bool pairs = fast && one_output && e.n_mirrors == 0 && dtype_size(odt) == 2;
+    char *obase = rp.c != nullptr ? rp.c : rp.out;
+    uint4 held = make_uint4(0u, 0u, 0u, 0u);
+    bool have_held = false;
+
     uint32_t next[8], cur[8];
     tmem_load_8_issue(taddr, next);
 #pragma unroll 1
@@ -721,7 +756,19 @@ __device__ __forceinline__ void epilogue_row(const EpiParams &e, uint32_t taddr,
         if (g + 1 < groups) {
             tmem_load_8_issue(taddr + static_cast<uint32_t>((g + 1) * 8), next);
         }
-        if (fast) {
+        if (pairs) {
+            const uint4 pk = epilogue_group8_packed<kAct, kDt>(e, cur, rp, g * step_bias, g * step_res, g);
+            char *dst = obase + g * 16;
+            if (have_held) {
+                store_32(dst - 16, held, pk);
+                have_held = false;
+            } else if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0 && g + 1 < groups) {
+                held = pk;
+                have_held = true;
+            } else {
+                *reinterpret_cast<uint4 *>(dst) = pk;
+            }
+        } else if (fast) {
             epilogue_group8_fast<kAct, kDt>(e, cur, rp, g * step_c, g * step_bias, g * step_res, g * step_out, g);
         } else if (row_ok) {
             epilogue_group8<kAct, (kDt < 0 ? -1 : (kDt == KUDNN_B200_F32 ? 1 : 0))>(e, cur, mi, n0 + g * 8);

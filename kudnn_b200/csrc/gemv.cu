@@ -718,13 +718,22 @@ cudaError_t launch_fma_m(const GemvParams &p, const GemvPlan &plan, cudaStream_t
         kernel<<<plan.grid, plan.block, plan.smem_bytes, stream>>>(p);                                            \
         break;                                                                                                    \
     }
-    switch (p.m) {
-        KB_FMA_CASE(1)
-        KB_FMA_CASE(2)
-        KB_FMA_CASE(3)
-        KB_FMA_CASE(4)
-        default:
-            return cudaErrorInvalidValue;
+    if constexpr (kDtype == KUDNN_B200_S8 || kDtype == KUDNN_B200_U8) {
+        // 8-bit weights take this kernel for a single activation row only
+        switch (p.m) {
+            KB_FMA_CASE(1)
+            default:
+                return cudaErrorInvalidValue;
+        }
+    } else {
+        switch (p.m) {
+            KB_FMA_CASE(1)
+            KB_FMA_CASE(2)
+            KB_FMA_CASE(3)
+            KB_FMA_CASE(4)
+            default:
+                return cudaErrorInvalidValue;
+        }
     }
 #undef KB_FMA_CASE
     return cudaGetLastError();
@@ -798,16 +807,14 @@ constexpr GemvShape kShapes[3] = {{512, 2}, {1024, 1}, {1024, 2}};
 constexpr int kStagedShape = 3;  // GemvPlan::shape of the staged-feed MMA kernel
 
 template <int kDtype, bool kFma>
-cudaError_t launch_shape(const GemvParams &p, const GemvPlan &plan, int shape, int unroll, cudaStream_t stream)
+cudaError_t launch_shape(const GemvParams &p, const GemvPlan &plan, int shape, cudaStream_t stream)
 {
 #define KB_SHAPE_CASE(S, T, B)                                                                       \
     case S:                                                                                          \
         if constexpr (kFma) {                                                                        \
-            return unroll >= 8 ? launch_fma_m<kDtype, 8, T, B>(p, plan, stream)                      \
-                               : launch_fma_m<kDtype, 4, T, B>(p, plan, stream);                     \
+            return launch_fma_m<kDtype, 4, T, B>(p, plan, stream);                                   \
         } else if constexpr (kDtype == KUDNN_B200_F16 || kDtype == KUDNN_B200_BF16) {                \
-            return unroll >= 8 ? launch_mma_rows<kDtype, 8, T, B>(p, plan, stream)                   \
-                               : launch_mma_rows<kDtype, 4, T, B>(p, plan, stream);                  \
+            return launch_mma_rows<kDtype, 4, T, B>(p, plan, stream);                                \
         }                                                                                            \
         return cudaErrorInvalidValue;
     switch (shape) {
@@ -1020,25 +1027,24 @@ cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const Gem
     p.blk_kb = static_cast<int>(pr.b_blocked_kpad / 64);
     const bool w8 = pr.b_dtype == KUDNN_B200_S8 || pr.b_dtype == KUDNN_B200_U8;
     const int dt = w8 ? pr.b_dtype : pr.a_dtype;
-    const int unroll = 4;
     if (plan.kernel == KUDNN_B200_KERNEL_GEMV_FMA) {
         const int vec = (dt == KUDNN_B200_F32) ? 4 : (w8 ? 16 : 8);
         p.kb = static_cast<int>((pr.k + 32 * vec - 1) / (32 * vec));
         p.kc = 0;
         p.total = pr.n * p.kb;
         if (dt == KUDNN_B200_F32) {
-            return launch_shape<KUDNN_B200_F32, true>(p, plan, plan.shape, unroll, stream);
+            return launch_shape<KUDNN_B200_F32, true>(p, plan, plan.shape, stream);
         }
         if (dt == KUDNN_B200_S8) {
-            return launch_shape<KUDNN_B200_S8, true>(p, plan, plan.shape, unroll, stream);
+            return launch_shape<KUDNN_B200_S8, true>(p, plan, plan.shape, stream);
         }
         if (dt == KUDNN_B200_U8) {
-            return launch_shape<KUDNN_B200_U8, true>(p, plan, plan.shape, unroll, stream);
+            return launch_shape<KUDNN_B200_U8, true>(p, plan, plan.shape, stream);
         }
         if (dt == KUDNN_B200_F16) {
-            return launch_shape<KUDNN_B200_F16, true>(p, plan, plan.shape, unroll, stream);
+            return launch_shape<KUDNN_B200_F16, true>(p, plan, plan.shape, stream);
         }
-        return launch_shape<KUDNN_B200_BF16, true>(p, plan, plan.shape, unroll, stream);
+        return launch_shape<KUDNN_B200_BF16, true>(p, plan, plan.shape, stream);
     }
     if (plan.shape == kStagedShape) {
         const long long kcs = ((pr.k + plan.ksplit - 1) / plan.ksplit + kStagedBlockK - 1) / kStagedBlockK * kStagedBlockK;
@@ -1054,9 +1060,9 @@ cudaError_t launch_gemv(const LinearProblem &pr, const GemvPlan &plan, const Gem
     p.kb = static_cast<int>(kc / block_k);
     p.total = ((pr.n + 7) / 8) * p.kb;
     if (pr.a_dtype == KUDNN_B200_F16) {
-        return launch_shape<KUDNN_B200_F16, false>(p, plan, plan.shape, unroll, stream);
+        return launch_shape<KUDNN_B200_F16, false>(p, plan, plan.shape, stream);
     }
-    return launch_shape<KUDNN_B200_BF16, false>(p, plan, plan.shape, unroll, stream);
+    return launch_shape<KUDNN_B200_BF16, false>(p, plan, plan.shape, stream);
 }
 
 }  // namespace kb

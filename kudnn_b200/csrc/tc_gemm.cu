@@ -4,15 +4,15 @@
 // (src/dnn/src/matmul_jit/MatrixComputation/kudnn_default_impl_fp16fp16f32f32.cpp:900-983) and the BLAS calls of
 // src/dnn/src/kudnn_gemm.cpp:157-227.
 //
-// Shape of one CTA (448 threads, persistent over output tiles, one CTA per SM):
+// Shape of one CTA (320 threads, persistent over output tiles, one CTA per SM):
 //   warp 0       producer: one lane issues the TMA loads of the A tile [128 x 128 B] and the B tile [rows x 128 B]
 //                of every k-block into the ring (4 to 6 stages), 128-byte swizzle, completion on an mbarrier
 //   warp 1       one lane issues tcgen05.mma (K = 32 bytes per instruction, four per k-block) into one of two TMEM
 //                accumulators and commits to the stage's "empty" barrier / the tile's "full" barrier; the warp also
 //                owns TMEM allocation
-//   warps 2..13  epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; three warps share a lane quarter and
-//                split the columns) 8 columns at a time, applies the post-GEMM chain and stores 16 bytes per tensor
-//                straight from registers (with output mirrors: 128-byte row pieces collected in shared memory); the
+//   warps 2..9   epilogue: a warp reads its 32 TMEM lanes (= 32 output rows; two warps share a lane quarter and
+//                split the columns) 8 columns at a time, applies the post-GEMM chain and stores 16 or 32 bytes per
+//                tensor straight from registers (with output mirrors: 128-byte row pieces collected in shared memory); the
 //                second accumulator lets this overlap the next tile's main loop
 // Three launch shapes (tc_make_plan): clusters of two CTAs on 256 x 256 tiles with cta_group::2 MMAs (large
 // problems), single CTAs on 128 x 256 / 128 x 128 tiles, and clusters of 2-8 CTAs that cut K of one 128 x 128 tile
@@ -40,7 +40,11 @@ namespace kb {
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kEpiWarps = 12;                      // two per scheduler: each hides the other's latencies
+// Two epilogue warps per scheduler (8 in all, 320 threads per CTA).  With three (12 warps, 128 registers each and some
+// spills) every shape measured 1.3-2.5 % slower on the same box: config 3's shape 208.8 against 203.7 us without
+// post-operation and 251 against 246 us with GELU and residual, config 2 290 against 285 us, the 32768-row layer 12.6
+// against 12.4 ms.
+constexpr int kEpiWarps = 8;
 constexpr int kTcThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA, warp 1: MMA, the rest: epilogue
 constexpr int kStageRowBytes = 128;  // one swizzle row: 64 16-bit or 32 32-bit elements
 constexpr int kABytes = kBM * kStageRowBytes;
@@ -77,6 +81,13 @@ struct TcParams {
     // Test hook for the timeout path: the producer of CTA 0 leaves out the loads of this k-block of its first work
     // item (-1 = never), so the MMA thread's wait for that stage runs into wait_limit.  Nothing faults or hangs.
     int skip_kb;
+    // Epilogue warps that work (4 or 8 of the kEpiWarps launched; the rest wait at the end of the kernel).  A light
+    // epilogue (no activation, relu or SiLU, one output) is finished by one warp per scheduler long before the next
+    // accumulator is ready, and every further warp only takes issue slots and power from the MMA and load threads;
+    // GELU or a second output need two per scheduler.  Same-box runs, 8 against 4 working warps: config 2 281.5
+    // against 276.5 us, a 4096-row shard of the large layer 1.432 against 1.405 ms, the whole layer 12.48 against
+    // 12.34 ms; with GELU and a residual 242 against 291 us (config 3's shape).
+    int epi_warps;
 };
 
 
@@ -1001,7 +1012,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tmem_full + a, 1);
-            mbar_init(tmem_empty + a, kPair ? 2 * kEpiWarps : kEpiWarps);  // pair: the epilogue warps of both CTAs
+            mbar_init(tmem_empty + a, kPair ? 2 * p.epi_warps : p.epi_warps);  // pair: the epilogue warps of both CTAs
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1155,13 +1166,15 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 }
             }
         }
-    } else {
+    } else if (warp < 2 + p.epi_warps) {
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: [32 * quarter, 32 * quarter + 32)
         const int row_in_tile = quarter * 32 + lane;
         const int part = (warp - 2) / 4;  // warps sharing a quarter split the tile's columns between them
         EpiParams e_batch;  // the epilogue tensors of the current batch entry (batched launches only)
-        float *warp_bias = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + 256) + (warp - 2) * kWarpBiasFloats;
+        // the bias slices of the working warps share the space laid out for kEpiWarps slices of kWarpBiasFloats
+        float *warp_bias = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(bars) + 256) +
+                           (warp - 2) * (kEpiWarps * kWarpBiasFloats / p.epi_warps);
         // Rows are collected into 128-byte pieces before they are stored only when peers receive copies: for local
         // memory alone the 16-byte stores straight from registers are faster (measured both ways).
         unsigned char *warp_stage = p.epi.n_mirrors > 0 ? reinterpret_cast<unsigned char *>(bars) + kTailBytes +
@@ -1186,7 +1199,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             const int tm = kPair ? 2 * (first_m + in_group % gsize) + static_cast<int>(pair_rank) : first_m + in_group % gsize;
             const int tn = in_group / gsize;
             // the warps that share a lane quarter split the tile's 8-column groups between them
-            constexpr int kParts = kEpiWarps / 4;
+            const int kParts = p.epi_warps / 4;
             const int piece_groups = width / 8;
             const int g_begin = part * piece_groups / kParts, g_end = (part + 1) * piece_groups / kParts;
             const long long n0 = static_cast<long long>(tn) * kBN + n_off + g_begin * 8;
@@ -1612,6 +1625,14 @@ cudaError_t launch_tc(const TcOperands &ops, const TcPlan &plan, const EpiParams
     p.wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : kDefaultWaitLimitCycles;
     // the test hook is honoured by the plain single-CTA shape only (no cluster partner is left half-signalled)
     p.skip_kb = (plan.pair == 0 && plan.splits == 1) ? skip_kblock : -1;
+    {
+        const bool sixteen = ops.kind == KUDNN_B200_F16 || ops.kind == KUDNN_B200_BF16;
+        const bool light = sixteen && plan.splits == 1 && ops.batch == 1 && epi.n_mirrors == 0 && epi.beta == 0.0f &&
+                           epi.res_op == KUDNN_B200_RES_NONE && epi.c_dtype == ops.kind &&
+                           (epi.has_bias == 0 || epi.bias_dtype == ops.kind) &&
+                           (epi.act == KUDNN_B200_ACT_NONE || epi.act == KUDNN_B200_ACT_RELU || epi.act == KUDNN_B200_ACT_SWISH);
+        p.epi_warps = light ? 4 : kEpiWarps;
+    }
     p.m = static_cast<int>(m);
     p.n = static_cast<int>(n);
     const int elems_per_row = kStageRowBytes / dtype_size(ops.kind);
